@@ -242,8 +242,9 @@ RA_API int ra_tile_plan_run(RaTilePlan* plan, int precision, const void* d_B, in
                             float* d_C, int N, void* stream);
 RA_API int ra_tile_plan_destroy(RaTilePlan* plan);
 /* Device status word of the plan's kernels (synchronises the device): 0 = ok; non-zero = a
- * bounded wait inside the bulk-copy ring variant gave up (1 = stage never filled). The
- * reference kernels have no waits and no counterpart. */
+ * bounded wait inside a kernel gave up (1 = a stage of the bulk-copy ring never filled,
+ * 3 = a tensor-core commit never arrived) and the output of that run is not valid. Reading a
+ * non-zero status clears it. The reference kernels have no waits and no counterpart. */
 RA_API int ra_tile_plan_device_status(RaTilePlan* plan, int* status);
 
 #ifdef __cplusplus

@@ -5,6 +5,7 @@
 #include <cuda_runtime.h>
 #include <cuda_fp16.h>
 
+#include <atomic>
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
@@ -51,6 +52,23 @@ int sm_count();   // cached cudaDevAttrMultiProcessorCount of the current device
             return (code);                                                    \
         }                                                                     \
     } while (0)
+
+// Function attributes (dynamic shared-memory limit, carve-out) belong to a (kernel, device)
+// pair, so a launcher keeps one bit per device ordinal and configures the kernel the first
+// time it runs on each device. Two host threads may both configure (the calls are
+// idempotent); neither can launch before its own configure call returned.
+template <typename F>
+inline cudaError_t configure_once_per_device(std::atomic<unsigned long long>& done, F&& configure) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    const unsigned long long bit = (dev >= 0 && dev < 64) ? (1ull << dev) : 0ull;   // ordinals >= 64: always configure
+    if (bit && (done.load(std::memory_order_acquire) & bit)) return cudaSuccess;
+    e = configure();
+    if (e != cudaSuccess) return e;
+    if (bit) done.fetch_or(bit, std::memory_order_release);
+    return cudaSuccess;
+}
 
 inline bool aligned16(const void* p) {
     return (reinterpret_cast<uintptr_t>(p) & 15u) == 0u;

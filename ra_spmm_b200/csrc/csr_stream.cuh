@@ -400,12 +400,12 @@ inline int launch_csr_stream(const StreamArgs& a, cudaStream_t st, long long tot
 #define RA_STREAM_LAUNCH(VV)                                                                   \
     do {                                                                                       \
         auto kern = csr_stream_kernel<VV, kMode>;                                              \
-        static bool configured = false;                                                        \
-        if (!configured) {                                                                     \
-            RA_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); \
-            RA_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, 100)); \
-            configured = true;                                                                 \
-        }                                                                                      \
+        static std::atomic<unsigned long long> configured{0};                                  \
+        RA_CUDA_TRY(configure_once_per_device(configured, [&]() -> cudaError_t {               \
+            cudaError_t e_ = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); \
+            if (e_ != cudaSuccess) return e_;                                                  \
+            return cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, 100); \
+        }));                                                                                   \
         kern<<<ctas, kStreamThreads, smem, st>>>(args);                                        \
     } while (0)
     if (V == 1) RA_STREAM_LAUNCH(1);
@@ -760,12 +760,12 @@ inline int launch_csr_stream_aligned(const StreamArgs& a, cudaStream_t st, long 
             ctas += cctas;                                                                     \
         }                                                                                      \
         auto kern = csr_stream_aligned_kernel<LL, VV, kMode>;                                  \
-        static bool configured = false;                                                        \
-        if (!configured) {                                                                     \
-            RA_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); \
-            RA_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, 100)); \
-            configured = true;                                                                 \
-        }                                                                                      \
+        static std::atomic<unsigned long long> configured{0};                                  \
+        RA_CUDA_TRY(configure_once_per_device(configured, [&]() -> cudaError_t {               \
+            cudaError_t e_ = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); \
+            if (e_ != cudaSuccess) return e_;                                                  \
+            return cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, 100); \
+        }));                                                                                   \
         kern<<<ctas, kStreamThreads, smem, st>>>(args);                                        \
     } while (0)
     switch (a.N) {

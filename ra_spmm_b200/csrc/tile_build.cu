@@ -441,6 +441,7 @@ extern "C" int ra_tile_plan_device_status(RaTilePlan* p, int* status)
     if (!p->d_status) return RA_OK;
     RA_CUDA_TRY(cudaDeviceSynchronize());
     RA_CUDA_TRY(cudaMemcpy(status, p->d_status, sizeof(int), cudaMemcpyDeviceToHost));
+    if (*status != 0) RA_CUDA_TRY(cudaMemset(p->d_status, 0, sizeof(int)));   // read and clear
     return RA_OK;
 }
 

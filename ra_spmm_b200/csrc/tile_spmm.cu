@@ -407,12 +407,23 @@ __device__ __forceinline__ void mbar_expect_tx(unsigned addr, unsigned bytes) {
 __device__ __forceinline__ void mbar_arrive(unsigned addr) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(addr) : "memory");
 }
-__device__ __forceinline__ bool mbar_wait(unsigned addr, unsigned parity) {
-    for (int i = 0; i < kSpinLimit; ++i) {
+__device__ __forceinline__ bool mbar_wait(unsigned addr, unsigned parity, int limit = kSpinLimit) {
+    for (int i = 0; i < limit; ++i) {
         unsigned ok;
         asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
                      : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
         if (ok) return true;
+    }
+    return false;
+}
+// Whole-warp form: the 32 lanes poll together and agree on the outcome, so the code after the
+// wait (warp-synchronous shared-memory reads) never runs with a part of the warp.
+__device__ __forceinline__ bool mbar_wait_warp(unsigned addr, unsigned parity, int limit) {
+    for (int i = 0; i < limit; ++i) {
+        unsigned ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
+        if (__all_sync(0xffffffffu, ok != 0u)) return true;
     }
     return false;
 }
@@ -424,7 +435,7 @@ __device__ __forceinline__ void bulk_copy_g2s(unsigned dst, const void* src, uns
 template <bool kTF32, int kMode>
 __global__ void __launch_bounds__(256)
 tile_spmm_tma_kernel(TileArgs a, const void* __restrict__ Bmat, int slices, int groups_total,
-                     int group_bytes, int* __restrict__ status)
+                     int group_bytes, int* __restrict__ status, int full_poll_limit)
 {
     constexpr int kMT     = kTF32 ? 2 : 4;
     constexpr int kElem   = kTF32 ? 4 : 2;
@@ -481,12 +492,12 @@ tile_spmm_tma_kernel(TileArgs a, const void* __restrict__ Bmat, int slices, int 
     if (producer) { ax = load_ax(0); ax_next = load_ax(4); }
     bool failed = false;
 
-    // producer warp: block rf -> stage rf % kStages
-    auto fetch = [&](int rf) {
+    // producer warp: block rf -> stage rf % kStages; false = the stage was never released (nothing issued)
+    auto fetch = [&](int rf) -> bool {
         if (rf >= ab + 4) { ax = ax_next; ab += 4; ax_next = load_ax(ab + 4); }
         const int st = rf & (kStages - 1);
         if (rf >= kStages) {                                  // wait until every warp released the stage
-            if (!mbar_wait(empty0 + 8 * st, (unsigned)(((rf >> 3) - 1) & 1))) { failed = true; return; }
+            if (!mbar_wait_warp(empty0 + 8 * st, (unsigned)(((rf >> 3) - 1) & 1), kSpinLimit)) { failed = true; return false; }
         }
         const int oct = (rf - ab) * 8;                        // lanes oct..oct+7 hold this block's columns
         const unsigned stage_s = ring_s + (unsigned)(st * stage_bytes);
@@ -498,13 +509,14 @@ tile_spmm_tma_kernel(TileArgs a, const void* __restrict__ Bmat, int slices, int 
         } else if (lane == ((oct + 8) & 31)) {
             bulk_copy_g2s(stage_s + (unsigned)(8 * row_stride), vals_base + (size_t)rf * 128, 128u, full0 + 8 * st);
         }
+        return true;
     };
 
     int rf = 0;
     if (producer) {
 #pragma unroll 1
         for (int i = 0; i < kStages - 1; ++i) {
-            if (rf < nb) { fetch(rf); ++rf; }
+            if (rf < nb && fetch(rf)) ++rf;
         }
     }
 
@@ -548,11 +560,11 @@ tile_spmm_tma_kernel(TileArgs a, const void* __restrict__ Bmat, int slices, int 
         while (rb < be) {
             const int st0 = rb & (kStages - 1);
             const unsigned s0 = ring_s + (unsigned)(st0 * stage_bytes);
-            if (!mbar_wait(full0 + 8 * st0, (unsigned)((rb >> 3) & 1))) { failed = true; break; }
+            if (!mbar_wait_warp(full0 + 8 * st0, (unsigned)((rb >> 3) & 1), full_poll_limit)) { failed = true; break; }
             if (!kTF32 && rb + 1 < be) {
                 const int st1 = (rb + 1) & (kStages - 1);
                 const unsigned s1 = ring_s + (unsigned)(st1 * stage_bytes);
-                if (!mbar_wait(full0 + 8 * st1, (unsigned)(((rb + 1) >> 3) & 1))) { failed = true; break; }
+                if (!mbar_wait_warp(full0 + 8 * st1, (unsigned)(((rb + 1) >> 3) & 1), full_poll_limit)) { failed = true; break; }
                 unsigned bf0, bf1;
                 asm volatile("ld.shared.u32 %0, [%1];" : "=r"(bf0) : "r"(s0 + 8 * row_stride + lane * 4));
                 asm volatile("ld.shared.u32 %0, [%1];" : "=r"(bf1) : "r"(s1 + 8 * row_stride + lane * 4));
@@ -569,8 +581,8 @@ tile_spmm_tma_kernel(TileArgs a, const void* __restrict__ Bmat, int slices, int 
                 __syncwarp();
                 if (lane == 0) { mbar_arrive(empty0 + 8 * st0); mbar_arrive(empty0 + 8 * st1); }
                 if (producer) {
-                    if (rf < nb) { fetch(rf); ++rf; }
-                    if (rf < nb && !failed) { fetch(rf); ++rf; }
+                    if (rf < nb && fetch(rf)) ++rf;
+                    if (rf < nb && !failed && fetch(rf)) ++rf;
                 }
                 rb += 2;
             } else {
@@ -606,7 +618,7 @@ tile_spmm_tma_kernel(TileArgs a, const void* __restrict__ Bmat, int slices, int 
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(empty0 + 8 * st0);
-                if (producer && rf < nb) { fetch(rf); ++rf; }
+                if (producer && rf < nb && fetch(rf)) ++rf;
                 rb += 1;
             }
             if (failed) break;
@@ -627,7 +639,17 @@ tile_spmm_tma_kernel(TileArgs a, const void* __restrict__ Bmat, int slices, int 
             }
         }
     }
-    if (failed && lane == 0) atomicExch(status, kStatusFullTimeout);
+    if (failed) {
+        if (lane == 0) atomicExch(status, kStatusFullTimeout);
+        // A warp that gave up still owns the bulk copies it issued: the producer waits, under the
+        // normal limit, until every stage it filled and nobody consumed has landed, so no copy is
+        // in flight into this CTA's shared memory when the CTA ends.
+        if (producer) {
+            for (int i = rb; i < rf; ++i) {
+                if (!mbar_wait_warp(full0 + 8 * (i & (kStages - 1)), (unsigned)((i >> 3) & 1), kSpinLimit)) break;
+            }
+        }
+    }
 }
 
 // ---------------------------------------------------------------------------
@@ -771,7 +793,8 @@ tile_spmm_tc5_kernel(TileArgs a, const __half* __restrict__ Bh, int groups_total
     for (int i = 0; i < kTcStages - 1; ++i) issue_fetch();
 
     int cstep = 0;                                            // K-steps consumed so far
-    int bad = 0;
+    int bad = 0;                                              // this thread saw a wait give up
+    int bad_cta = 0;                                          // CTA-uniform: only ever set from a barrier reduction
     // Several units accumulate side by side in TMEM (16 columns per unit and panel) and are
     // written out together, so the wait for the tensor core and the CTA barrier that protects
     // the accumulators are paid once per batch instead of once per unit.
@@ -789,7 +812,7 @@ tile_spmm_tc5_kernel(TileArgs a, const __half* __restrict__ Bh, int groups_total
             const int stage = cstep % kTcStages;
             cp_async_wait<kTcStages - 2>();
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            if (__syncthreads_or(bad)) { bad = 1; break; }
+            if (__syncthreads_or(bad)) { bad_cta = 1; break; }
             if (tid == 0) {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const unsigned st = smem_s + (unsigned)(stage * stage_bytes);
@@ -811,7 +834,10 @@ tile_spmm_tc5_kernel(TileArgs a, const __half* __restrict__ Bh, int groups_total
             }
             issue_fetch();
         }
-        if (bad) break;
+        // Only the CTA-uniform flag leaves the loop: a thread whose own wait gave up on the last
+        // K-step of a unit carries `bad` to the next barrier reduction, so every thread reaches
+        // the same barriers and the aligned TMEM instructions together.
+        if (bad_cta) break;
         pend_u[slot & 3] = u; pend_steps[slot & 3] = nsteps;
         ++slot;
         if (slot < units_per_batch && u + 1 < u_hi) continue;
@@ -821,9 +847,10 @@ tile_spmm_tc5_kernel(TileArgs a, const __half* __restrict__ Bh, int groups_total
             const int last = cstep - 1;
             if (!mbar_wait(bar0 + 8 * (last % kTcStages), (unsigned)((last / kTcStages) & 1))) bad = 1;
         }
+        if (__syncthreads_or(bad)) { bad_cta = 1; break; }    // nobody reads TMEM after a failed wait
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
-        for (int q = 0; q < slot && !bad; ++q) {
+        for (int q = 0; q < slot; ++q) {
             const int uu = pend_u[q & 3];
             float* base = a.C;
             int wrow0 = uu * kWindowRows;
@@ -858,12 +885,12 @@ tile_spmm_tc5_kernel(TileArgs a, const __half* __restrict__ Bh, int groups_total
         slot = 0;
         // every thread has read its accumulators before the next batch overwrites them
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        if (__syncthreads_or(bad)) { bad = 1; break; }
+        __syncthreads();
     }
     cp_async_wait<0>();
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (bad && tid == 0) atomicExch(status, kStatusMmaTimeout);
+    if (bad_cta && tid == 0) atomicExch(status, kStatusMmaTimeout);
     if (warp == 0) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 64;" :: "r"(tmem) : "memory");
     }
@@ -1064,11 +1091,10 @@ static int launch_tile(const TileArgs& a, const void* B, bool staged, cudaStream
             long long ctas5 = (long long)sm_count() * per_sm * 3;
             ctas5 = std::min(ctas5, std::max<long long>(1, weight / 48));
             auto kern5 = tile_spmm_tc5_kernel<kMode>;
-            static bool attr_set5 = false;
-            if (!attr_set5) {
-                RA_CUDA_TRY(cudaFuncSetAttribute(kern5, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
-                attr_set5 = true;
-            }
+            static std::atomic<unsigned long long> attr_set5{0};
+            RA_CUDA_TRY(configure_once_per_device(attr_set5, [&]() {
+                return cudaFuncSetAttribute(kern5, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+            }));
             kern5<<<(unsigned)ctas5, kTcThreads, smem5, st>>>(a, static_cast<const __half*>(B), (int)ctas5, panels, status);
             RA_KERNEL_CHECK();
             return RA_OK;
@@ -1088,31 +1114,32 @@ static int launch_tile(const TileArgs& a, const void* B, bool staged, cudaStream
             const int ctas_t = (int)((groups_t + groups_per_cta - 1) / groups_per_cta);
             groups_t = (long long)ctas_t * groups_per_cta;
             auto kern_t = tile_spmm_tma_kernel<kTF32, kMode>;
-            static bool attr_set_t = false;
-            if (!attr_set_t) {
-                RA_CUDA_TRY(cudaFuncSetAttribute(kern_t, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
-                attr_set_t = true;
-            }
+            static std::atomic<unsigned long long> attr_set_t{0};
+            RA_CUDA_TRY(configure_once_per_device(attr_set_t, [&]() {
+                return cudaFuncSetAttribute(kern_t, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+            }));
             RA_REQUIRE(smem_t <= 100 * 1024, RA_ERR_UNSUPPORTED, "tile SpMM: N=%d too wide for the staged kernel", a.N);
-            kern_t<<<ctas_t, warps * 32, smem_t, st>>>(a, B, slices, (int)groups_t, group_bytes, status);
+            // RA_TILE_TMA_POLL_LIMIT (tests only): polls a consumer warp spends on a stage before it
+            // gives up and reports through the status word; every other wait keeps the normal limit
+            const char* poll_env = std::getenv("RA_TILE_TMA_POLL_LIMIT");
+            const int poll_limit = poll_env ? std::max(1, std::atoi(poll_env)) : kSpinLimit;
+            kern_t<<<ctas_t, warps * 32, smem_t, st>>>(a, B, slices, (int)groups_t, group_bytes, status, poll_limit);
             RA_KERNEL_CHECK();
             return RA_OK;
         }
         if (kTF32 && depth == 4) {
             auto kern = tile_spmm_kernel<kTF32, kMode, kZC, kTF32 ? 4 : 8>;
-            static bool attr_set4 = false;
-            if (!attr_set4) {
-                RA_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 4 * stage));
-                attr_set4 = true;
-            }
+            static std::atomic<unsigned long long> attr_set4{0};
+            RA_CUDA_TRY(configure_once_per_device(attr_set4, [&]() {
+                return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 4 * stage);
+            }));
             kern<<<ctas, warps * 32, smem, st>>>(a, B, slices, (int)groups);
         } else {
             auto kern = tile_spmm_kernel<kTF32, kMode, kZC, 8>;
-            static bool attr_set = false;
-            if (!attr_set) {
-                RA_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 8 * stage));
-                attr_set = true;
-            }
+            static std::atomic<unsigned long long> attr_set{0};
+            RA_CUDA_TRY(configure_once_per_device(attr_set, [&]() {
+                return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 8 * stage);
+            }));
             kern<<<ctas, warps * 32, smem, st>>>(a, B, slices, (int)groups);
         }
     } else {

@@ -1,26 +1,24 @@
 """Fits runtime_cost_model.json on the current GPU: log-linear setup and warm cost per
 kernel over [1, log1p M, log1p nnz, log1p N, log1p nnz*N, log1p avg, log1p cv]
-(ra_runtime_router.py:24-32), from timings of seeded synthetic graphs.
+(the design row of ra_runtime_router.py:24-32), from timings of seeded synthetic graphs.
 
     python -m ra_spmm_b200.fit_cost_model [--out path]"""
 from __future__ import annotations
 
 import argparse
-import json
 import time
-from pathlib import Path
 
 import numpy as np
 import torch
 
 from . import generators as G
 from .harness import build_kernel_plan, measure_cuda_exec_ms, run_planned_kernel
-from .runtime_router import DEFAULT_MODEL, KERNELS, feature_vector
+from .cost_model import PORTFOLIO as KERNELS, SHIPPED_MODEL, CostModel, design_rows
 
 
 def graphs():
     yield "er16", G.erdos_renyi_fixed_degree(4096, 4096, 16, 0)
-    yield "er8_64k", G.erdos_renyi_fixed_degree(65536, 65536, 8, 1) if False else G.rmat_graph(13, 8, seed=11)
+    yield "rmat13", G.rmat_graph(13, 8, seed=11)
     for n, s in ((20000, 1), (100000, 2), (400000, 3)):
         yield f"cl{n}", G.chung_lu_power_law(n=n, seed=s)
     for sc, ef, s in ((14, 16, 4), (16, 8, 5), (17, 16, 6)):
@@ -31,7 +29,7 @@ def graphs():
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--out", default=str(DEFAULT_MODEL))
+    ap.add_argument("--out", default=str(SHIPPED_MODEL))
     args = ap.parse_args()
     dev = torch.device("cuda", 0)
     rows = {k: [] for k in KERNELS}
@@ -41,7 +39,7 @@ def main():
         avg, cv = float(deg.mean()), float(deg.std() / max(deg.mean(), 1e-9))
         for N in (32, 64, 128, 256):
             B = torch.randn(a.K, N, device=dev)
-            x = feature_vector(a.M, a.nnz, N, avg, cv)
+            x = design_rows(a.M, a.nnz, N, avg, cv)
             for k in KERNELS:
                 torch.cuda.synchronize(); t0 = time.perf_counter()
                 plan = build_kernel_plan(k, rp, ci, va, a.M, a.K, N)
@@ -50,14 +48,8 @@ def main():
                 rows[k].append((x, setup_ms, warm_ms))
                 del plan
         print(name, a.M, a.nnz, flush=True)
-    model = {"device": torch.cuda.get_device_name(0), "features": "1, log1p M, log1p nnz, log1p N, log1p nnz*N, log1p avg, log1p cv",
-             "samples_per_kernel": len(rows[KERNELS[0]]), "kernels": {}}
-    for k, r in rows.items():
-        X = np.array([x for x, _, _ in r])
-        fit = lambda y: np.linalg.lstsq(X, np.log(np.array(y)), rcond=None)[0].tolist()
-        model["kernels"][k] = {"setup_coefficients": fit([s for _, s, _ in r]),
-                               "warm_coefficients": fit([w for _, _, w in r])}
-    Path(args.out).write_text(json.dumps(model, indent=1))
+    meta = {"device": torch.cuda.get_device_name(0), "samples_per_kernel": len(rows[KERNELS[0]])}
+    CostModel.fit(rows, meta).save(args.out)
     print("wrote", args.out)
 
 

@@ -23,7 +23,7 @@ MAIN_KERNELS = ["CSR_DIRECT", "ZERO_OVERHEAD_CSR", "TC_DIRECT", "COMMUNITY_TC", 
 
 
 # ---- cuSPARSE pass-through (vendor library; lives beside the entry points it mirrors) ----
-CusparsePlan = m.CusparsePlan
+CusparsePlan = m.CuSparsePlan
 make_cusparse_plan = m.make_cusparse_plan
 run_cusparse_plan = m.run_cusparse_plan
 spmm_cusparse = m.spmm_cusparse
@@ -43,7 +43,7 @@ def build_kernel_plan(kernel, rowptr, colind, vals, M, K, N):
     if fam == "SEGMENT_HYBRID":
         return m.make_segment_hybrid_plan(rowptr, colind, vals, M, K, N)
     if fam == "CUSPARSE":
-        return make_cusparse_plan(rowptr, colind, vals, M, K)
+        return m.CuSparsePlan(rowptr, colind, vals, K)
     raise ValueError(f"Kernel has no reusable custom plan: {kernel}")
 
 

@@ -33,7 +33,8 @@ __all__ = [
     "make_community_tc_plan", "run_community_tc_plan", "run_community_tc_plan_tf32",
     "make_segment_hybrid_plan", "run_segment_hybrid_plan", "run_segment_hybrid_plan_tf32",
     "make_router_plan", "run_router_plan", "gpu_info_next",
-    "spmm_cusparse", "make_cusparse_plan", "run_cusparse_plan",
+    "spmm_cusparse", "spmm_cusparse_fp16", "make_cusparse_plan", "run_cusparse_plan",
+    "benchmark_cusparse", "benchmark_cusparse_cold", "benchmark_cusparse_fp16", "benchmark_cusparse_fp16_cold",
     "RAZeroOverheadPlan", "RATcDirectPlan", "RACommunityTCPlan", "RASegmentHybridPlan",
 ]
 
@@ -84,6 +85,7 @@ def spmm_csr_direct(rowptr, colind, vals, B):
     _check_dense_b(B)
     M = rowptr.shape[0] - 1
     K, N = B.shape
+    # the kernel gathers B[colind]; the binding cannot see K, so the caller's B states it
     C_out = torch.empty((M, N), dtype=torch.float32, device=B.device)
     with torch.cuda.device(B.device):
         st = _lib().ra_csr_direct_spmm(
@@ -184,6 +186,10 @@ def run_zero_overhead_plan(plan, rowptr, colind, vals, B):
     _check_dense_b(B)
     if plan is None or not getattr(plan, "valid", False):
         raise RuntimeError("Invalid ZeroOverhead plan")
+    if B.shape[0] != plan.K:
+        raise RuntimeError(f"B has {B.shape[0]} rows but the plan was built for K={plan.K}")
+    if rowptr.numel() != plan.M + 1:
+        raise RuntimeError(f"rowptr has {rowptr.numel()} entries but the plan was built for M={plan.M}")
     M, N = plan.M, B.shape[1]
     C_out = torch.empty((M, N), dtype=torch.float32, device=B.device)
     with torch.cuda.device(B.device):
@@ -320,6 +326,8 @@ def _run_tile_plan(plan, B, precision, what):
     _check_dense_b(B, allow_half=(precision == _capi.PRECISION_FP16))
     if plan is None or not getattr(plan, "valid", False):
         raise RuntimeError(f"Invalid {what} plan")
+    if B.shape[0] != plan.K:
+        raise RuntimeError(f"B has {B.shape[0]} rows but the plan was built for K={plan.K}")
     M, N = plan.M, B.shape[1]
     C_out = torch.empty((M, N), dtype=torch.float32, device=B.device)
     b_dtype = _capi.DTYPE_F16 if B.dtype == torch.float16 else _capi.DTYPE_F32
@@ -464,27 +472,108 @@ def make_router_plan(rowptr, colind, vals, M, K, N, portfolio="MAIN"):
 
 
 # ---------------------------------------------------------------------------
-# cuSPARSE guardrail (bindings/ra_bindings.cpp:431-615, 2342-2391): the vendor library
-# behind rule 5's CUSPARSE route and the harness reference. A pass-through to the
-# cuSPARSE SpMM that torch exposes for CSR tensors, not one of this library's kernels.
+# cuSPARSE guardrail and harness reference (bindings/ra_bindings.cpp:431-615, 838-1037,
+# 2342-2391): the vendor library behind rule 5's CUSPARSE route, the correctness reference of
+# the sweep drivers and their external baseline. Pass-throughs to the cuSPARSE SpMM that torch
+# exposes for CSR tensors - library calls, not kernels of this package.
 # ---------------------------------------------------------------------------
-class CusparsePlan:
-    def __init__(self, rowptr, colind, vals, M, K):
-        self.A = torch.sparse_csr_tensor(rowptr, colind, vals, size=(int(M), int(K)))
+class CuSparsePlan:
+    """Reusable CSR operand (CuSparsePlanWrapper, bindings/ra_bindings.cpp:2374-2386)."""
+
+    def __init__(self, rowptr, colind, vals, K, half=False):
+        M = rowptr.shape[0] - 1
+        v = vals.to(torch.float16) if half else vals
+        self.A = torch.sparse_csr_tensor(rowptr, colind, v, size=(int(M), int(K)))
+        self.half = half
         self.valid = True
+        self.algorithm = "torch.sparse.mm (cuSPARSE CSR SpMM)"
 
 
-def make_cusparse_plan(rowptr, colind, vals, M, K, N=None):
-    return CusparsePlan(rowptr, colind, vals, M, K)
+CusparsePlan = CuSparsePlan
+
+
+def make_cusparse_plan(rowptr, colind, vals, B):
+    """`B` is a same-shape dense operand (only its row count is read), as in the reference."""
+    _check_csr_tensors(rowptr, colind, vals)
+    K = B.shape[0] if torch.is_tensor(B) else int(B)
+    return CuSparsePlan(rowptr, colind, vals, K)
 
 
 def run_cusparse_plan(plan, B):
+    if plan.half:
+        return torch.sparse.mm(plan.A, B.to(torch.float16)).float()
     return torch.sparse.mm(plan.A, B)
 
 
 def spmm_cusparse(rowptr, colind, vals, B):
-    M = rowptr.shape[0] - 1
-    return run_cusparse_plan(make_cusparse_plan(rowptr, colind, vals, M, B.shape[0]), B)
+    return run_cusparse_plan(make_cusparse_plan(rowptr, colind, vals, B), B)
+
+
+def spmm_cusparse_fp16(rowptr, colind, vals, B):
+    """Precision-matched vendor baseline: A and B rounded to fp16, result returned as fp32."""
+    _check_csr_tensors(rowptr, colind, vals)
+    return run_cusparse_plan(CuSparsePlan(rowptr, colind, vals, B.shape[0], half=True), B)
+
+
+def _event_ms(fn, warmup, iters):
+    # measure_cuda_exec_ms, bench/benchmark.cpp:39-67
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def _cusparse_timing(label, plan_ms, exec_ms, nnz, N, main):
+    return {"plan_ms": plan_ms, "exec_ms": exec_ms, "total_ms": plan_ms + exec_ms,
+            "gflops": (2.0 * nnz * N / (exec_ms * 1e6)) if exec_ms > 0 else 0.0,
+            "path": label, "in_main_portfolio": main, "legacy_baseline": False,
+            "external_baseline": not main, "cusparse_algorithm": "torch.sparse.mm (cuSPARSE CSR SpMM)",
+            "preprocess_ms": plan_ms}
+
+
+def _bench_cusparse(rowptr, colind, vals, B, half, warmup, iters, cold):
+    _check_csr_tensors(rowptr, colind, vals)
+    _check_dense_b(B)
+    nnz, N = colind.numel(), B.shape[1]
+    label = "CUSPARSE_FP16" if half else "CUSPARSE"
+    iters = max(1, int(iters))
+    if not cold:
+        plan = CuSparsePlan(rowptr, colind, vals, B.shape[0], half=half)
+        Bop = B.to(torch.float16) if half else B
+        ms = _event_ms(lambda: torch.sparse.mm(plan.A, Bop), int(warmup), iters)
+        return _cusparse_timing(label, 0.0, ms, nnz, N, False)
+    plan_sum = exec_sum = 0.0
+    for _ in range(iters):                      # state construction timed on the host, one run on the device
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        plan = CuSparsePlan(rowptr, colind, vals, B.shape[0], half=half)
+        Bop = B.to(torch.float16) if half else B
+        torch.cuda.synchronize()
+        plan_sum += (time.perf_counter() - t0) * 1e3
+        exec_sum += _event_ms(lambda: torch.sparse.mm(plan.A, Bop), 0, 1)
+    return _cusparse_timing(label, plan_sum / iters, exec_sum / iters, nnz, N, not half)
+
+
+def benchmark_cusparse(rowptr, colind, vals, B, warmup=3, iters=10):
+    return _bench_cusparse(rowptr, colind, vals, B, False, warmup, iters, False)
+
+
+def benchmark_cusparse_cold(rowptr, colind, vals, B, iters=10):
+    return _bench_cusparse(rowptr, colind, vals, B, False, 0, iters, True)
+
+
+def benchmark_cusparse_fp16(rowptr, colind, vals, B, warmup=3, iters=10):
+    return _bench_cusparse(rowptr, colind, vals, B, True, warmup, iters, False)
+
+
+def benchmark_cusparse_fp16_cold(rowptr, colind, vals, B, iters=10):
+    return _bench_cusparse(rowptr, colind, vals, B, True, 0, iters, True)
 
 
 def run_router_plan(plan_dict, rowptr, colind, vals, B):

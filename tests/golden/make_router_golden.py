@@ -1,7 +1,7 @@
 """Generates tests/golden/router_known_answers.json.
 
-Run in a checkout that has the reference tree (default /root/reference) and
-oracle/_ref built (make -C oracle). For every (graph, N) row of the reference's
+Usage: make_router_golden.py <RA-SpMM checkout> (or RA_REFERENCE_DIR in the environment), with
+oracle/_ref built (make -C oracle REF=<checkout>). For every (graph, N) row of the reference's
 published sweep (fgcs_results/revision/tf32/final_fair_v3.csv: M, nnz, cv_d;
 router_quality_v8.csv: the routed kernel) it records the inputs (M, nnz, cv_d, N)
 and three answers: the label the reference published, the label of the
@@ -10,13 +10,14 @@ reference's C++ route_dispatch compiled from source. Dataset names are not kept.
 """
 import csv
 import json
+import os
 import sys
 from pathlib import Path
 
 import numpy as np
 
 ROOT = Path(__file__).resolve().parents[2]
-REF = Path(sys.argv[1]) if len(sys.argv) > 1 else Path("/root/reference")
+REF = Path(sys.argv[1] if len(sys.argv) > 1 else os.environ["RA_REFERENCE_DIR"])
 sys.path.insert(0, str(ROOT))
 sys.path.insert(0, str(REF))
 

@@ -9,7 +9,7 @@ from oracle import ra_oracle as O
 from ra_spmm_b200 import generators as G
 from ra_spmm_b200 import harness as H
 from ra_spmm_b200 import ra_spmm
-from ra_spmm_b200 import runtime_router as RR
+from ra_spmm_b200 import cost_model as CM
 
 pytestmark = pytest.mark.gpu
 
@@ -56,22 +56,19 @@ def test_plan_checksums_are_reproducible_and_match_the_oracle(graph):
     assert c1["win_rows"] == f"{H.fnv1a64(wr):016x}"
 
 
-def test_lifecycle_router_with_a_cost_model(graph, tmp_path):
+def test_lifecycle_choice_from_the_cost_model_runs(graph):
+    """Kernel ranked best by the shipped model for 1 and for 1000 calls is built and run through
+    the label-driven plan helpers, as the reference's lifecycle router does with its choice."""
     a, rp, ci, va, B = graph
-    # a model in which ZERO_OVERHEAD_CSR has no setup cost and tile kernels a large one
-    flat = lambda ms: [float(np.log(ms)), 0, 0, 0, 0, 0, 0]
-    model = {"kernels": {"CSR_DIRECT": {"setup_coefficients": flat(1e-3), "warm_coefficients": flat(1.0)},
-                         "ZERO_OVERHEAD_CSR": {"setup_coefficients": flat(0.1), "warm_coefficients": flat(0.5)},
-                         "TC_DIRECT": {"setup_coefficients": flat(50.0), "warm_coefficients": flat(0.25)}}}
-    path = tmp_path / "model.json"
-    path.write_text(json.dumps(model))
-    cold = RR.make_runtime_router_plan(rp, ci, va, a.M, a.K, 64, assume_cold=True, model_path=path)
-    assert cold.chosen_path == "ZERO_OVERHEAD_CSR"
-    many = RR.make_runtime_router_plan(rp, ci, va, a.M, a.K, 64, expected_calls=1000, model_path=path)
-    assert many.chosen_path == "TC_DIRECT"
-    C = many.run(rp, ci, va, B)
+    plan = ra_spmm.make_router_plan(rp, ci, va, a.M, a.K, 64)
+    fv = plan["feature_values"]
+    x = CM.design_rows(a.M, a.nnz, 64, fv["avg_nnz_per_row"], fv["degree_cv"])
+    model = CM.CostModel.load()
     ref = ra_spmm.spmm_csr_direct(rp, ci, va, B)
-    assert float((C - ref).norm() / ref.norm()) < 5e-3
-    if RR.DEFAULT_MODEL.exists():            # the fitted model shipped with the package
-        plan = RR.make_runtime_router_plan(rp, ci, va, a.M, a.K, 64, expected_calls=100)
-        assert plan.chosen_path in RR.KERNELS
+    for calls in (1, 1000):
+        est = model.lifecycle_ms(x, calls, allowed=plan["feasible_by_path"])
+        best = min(est, key=est.get)
+        assert best in CM.PORTFOLIO
+        kp = H.build_kernel_plan(best, rp, ci, va, a.M, a.K, 64)
+        C = H.run_planned_kernel(best, kp, rp, ci, va, B)
+        assert float((C - ref).norm() / ref.norm()) < 5e-3
