@@ -2,17 +2,22 @@
 """Benchmark of the SpMM hot path: warm SpMM GFLOP/s (2*nnz*N) and fraction of the
 HBM roofline on 1/2/4/8 B200s of one node.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--config C2] [--kernel routed]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--config C4] [--kernel named]
     python bench.py --impl reference ...     # torch.sparse.mm on the host cores
 
 A step is one SpMM (plan already built, as in the reference's warm protocol,
-ra_real_graph_eval.py:37-38,210-221). Default workload: configuration 2 of
-BASELINE.json (Chung-Lu power-law graph, 1,048,576 nodes, N=128, fp32) through the
-kernel the router picks for it (ZERO_OVERHEAD_CSR). With N>1 ranks (torchrun) the
-rows of A are split into nnz-balanced contiguous blocks, B is replicated (--shard grid
-adds column panels of B), each rank writes its own slab of C and no collective runs on
-the data path; the total work is fixed (strong scaling) and the reported time is the
-max over ranks.
+ra_real_graph_eval.py:37-38,210-221). Default workload: configuration 4 of
+BASELINE.json, the largest single SpMM (R-MAT scale 22, 128 M nonzeros, N=64), through the
+kernel BASELINE.json names for it (SEGMENT_HYBRID on the TF32 path); the kernel the router
+picks is timed beside it, and so are configurations 2 and 3, in the `also` block of the
+same JSON line (each with 50 warm-ups + 200 timed launches, the reference's WARMUP /
+TIMED_ITERS). With N>1 ranks (torchrun) the rows of A are split into contiguous row blocks
+whose boundaries are tuned at plan time from the measured time of each rank's block, B is
+replicated, each rank writes its own slab of C and no collective runs on the data path of
+the device-timed SpMM; the total work is fixed (strong scaling) and the reported time is
+the max over ranks. The end-to-end path uploads each rank's K/N row slab of B from pinned
+host memory, rebuilds the replica with one NCCL all-gather over NVLink, runs the SpMM and
+copies the rank's slab of C back.
 Prints ONE JSON line on rank 0.
 """
 from __future__ import annotations
@@ -41,6 +46,10 @@ CONFIG_DESC = {
     "C4": "R-MAT scale 22, edge factor 16, symmetrised + dedup, N=64 fp32 on the TF32 path, seed 3",
     "C5": "GCN-normalised SBM 2,449,029 nodes, mean degree 50, N=256 fp32, seed 123 (single SpMM)",
 }
+DEFAULT_CONFIG = "C4"
+# (configuration, kernel selector) timed beside the headline in the same run
+ALSO = [("C4", "routed"), ("C2", "named"), ("C3", "named"), ("C3", "routed")]
+TOL = {"fp32": 1e-5, "tile": 5e-3}
 
 
 def parse_args():
@@ -49,21 +58,25 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--config", default="C2", choices=list(CONFIG_KERNEL))
+    ap.add_argument("--config", default=DEFAULT_CONFIG, choices=list(CONFIG_KERNEL))
     ap.add_argument("--kernel", default="named",
                     help="named (the kernel BASELINE.json names for the config) | routed | CSR_DIRECT | ZERO_OVERHEAD_CSR | TC_DIRECT[_TF32] | COMMUNITY_TC[_TF32] | "
                          "SEGMENT_HYBRID[_TF32]")
     ap.add_argument("--scale", type=float, default=1.0, help="shrink the graph (debugging only)")
     ap.add_argument("--e2e-steps", type=int, default=10)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--also", default="auto", choices=["auto", "on", "off"],
+                    help="time the other configurations / kernels too (auto: when the default configuration runs at full size)")
+    ap.add_argument("--inner-warmup", type=int, default=50, help="warm-up launches of each `also` entry")
+    ap.add_argument("--inner-iters", type=int, default=200, help="timed launches of each `also` entry")
     ap.add_argument("--row-weight", type=float, default=None,
-                    help="multi-GPU row partition: nonzeros that one row is worth when balancing the blocks "
-                         "(default: 3 for the CSR kernels, measured best of 1/3/6 on configurations 2 and 4 at "
-                         "2 GPUs; 1 for the tile kernels)")
-    ap.add_argument("--shard", default="rows", choices=["rows", "grid"],
-                    help="multi-GPU partition: rows = nnz-balanced row blocks, B replicated (default); grid = row "
-                         "blocks x column panels of B when B exceeds the L2 (measured slower on C2 at 2 GPUs: "
-                         "0.43 vs 0.34 ms, but halves the host-to-device bytes)")
+                    help="multi-GPU row partition: nonzeros that one row is worth in the first cut of the blocks "
+                         "(default: 3 for the CSR kernels, 1 for the tile kernels); the cut is then tuned from measured times")
+    ap.add_argument("--balance-rounds", type=int, default=3,
+                    help="multi-GPU: rounds of measuring every rank's block and moving the boundaries")
+    ap.add_argument("--emulate-ranks", type=int, default=0,
+                    help="diagnostic, one GPU: cut the rows as for this many ranks, time the blocks one after the other "
+                         "and report the balance (no JSON contract line)")
     return ap.parse_args()
 
 
@@ -128,9 +141,20 @@ class ClockSampler:
                 "reasons": sorted(reasons)}
 
 
-def load_config(name, scale):
+def load_config(name, scale, rank=0, dist_on=False):
+    """Graph + dense operand of a configuration. Rank 0 generates (or loads the on-disk cache)
+    first; the other ranks load what it cached."""
     from ra_spmm_b200 import generators as G
-    a, N, b_dtype = G.make_config(name, scale)
+    if dist_on:
+        import torch.distributed as dist
+        if rank == 0:
+            out = G.cached_config(name, scale)
+        dist.barrier()
+        if rank != 0:
+            out = G.cached_config(name, scale)
+    else:
+        out = G.cached_config(name, scale)
+    a, N, b_dtype = out
     B = G.dense(a.K, N, G.CONFIG_SEEDS[name], b_dtype)
     return a, N, B, b_dtype
 
@@ -146,9 +170,10 @@ def strided_row_sample(a, stride):
     return rp, a.colind[idx].astype(np.int64), a.vals[idx]
 
 
-def cpu_spmm_bench(a, B, steps, warmup, budget_s=20.0):
+def cpu_spmm_bench(a, B, steps, warmup, budget_s=20.0, keep_result=False):
     """torch.sparse.mm on a CPU CSR tensor (the reference harness's CPU-runnable
-    operator, test_ra.py:106-172), all host threads, on a bounded strided row sample."""
+    operator, test_ra.py:106-172), all host threads, on a bounded strided row sample.
+    Returns a dict; with keep_result the sample's rows and its product stay in it."""
     import torch
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
@@ -163,21 +188,24 @@ def cpu_spmm_bench(a, B, steps, warmup, budget_s=20.0):
 
     stride = 1
     A, nnz_s = make(stride)
-    t0 = time.perf_counter(); torch.sparse.mm(A, Bf); t_full = time.perf_counter() - t0
+    t0 = time.perf_counter(); out = torch.sparse.mm(A, Bf); t_full = time.perf_counter() - t0
     per_step_budget = budget_s / max(1, steps + warmup)
     if t_full > per_step_budget:
         stride = int(min(a.M, max(2, round(t_full / per_step_budget))))
         A, nnz_s = make(stride)
     for _ in range(warmup):
-        torch.sparse.mm(A, Bf)
+        out = torch.sparse.mm(A, Bf)
     times = []
     for _ in range(steps):
-        t0 = time.perf_counter(); torch.sparse.mm(A, Bf); times.append(time.perf_counter() - t0)
+        t0 = time.perf_counter(); out = torch.sparse.mm(A, Bf); times.append(time.perf_counter() - t0)
     total = sum(times)
-    gflops = 2.0 * nnz_s * N * steps / total / 1e9
-    sample = (f"torch.sparse.mm CSR fp32, rows 0::{stride} of the workload ({A.shape[0]} rows, {nnz_s} nnz), "
-              f"{steps} passes after {warmup} warm-up")
-    return gflops, total / steps * 1e3, cores, sample
+    res = {"gflops": 2.0 * nnz_s * N * steps / total / 1e9, "ms": total / steps * 1e3, "cores": cores,
+           "stride": stride,
+           "sample": (f"torch.sparse.mm CSR fp32, rows 0::{stride} of the workload ({A.shape[0]} rows, {nnz_s} nnz), "
+                      f"{steps} passes after {warmup} warm-up")}
+    if keep_result:
+        res["result"] = out
+    return res
 
 
 def run_reference(args):
@@ -185,16 +213,16 @@ def run_reference(args):
     if rank != 0:
         return
     a, N, B, b_dtype = load_config(args.config, args.scale)
-    gflops, ms, cores, sample = cpu_spmm_bench(a, B, args.steps, max(args.warmup, 1), budget_s=120.0)
+    r = cpu_spmm_bench(a, B, args.steps, max(args.warmup, 1), budget_s=120.0)
     line = {
-        "metric": METRIC, "value": gflops, "unit": UNIT, "impl": "reference", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "metric": METRIC, "value": r["gflops"], "unit": UNIT, "impl": "reference", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms"], "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": f"{args.config}: {CONFIG_DESC[args.config]}", "kernel": "torch.sparse.mm (CPU, CSR)",
                    "note": "reference arm = the reference harness's CPU operator on the host cores; "
                            "each step is a bounded strided row sample of the workload"},
-        "cpu_baseline": {"value": gflops, "unit": UNIT, "cores": cores, "kind": "reference", "sample": sample},
-        "e2e": {"value": gflops, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "cpu_baseline": {"value": r["gflops"], "unit": UNIT, "cores": r["cores"], "kind": "reference", "sample": r["sample"]},
+        "e2e": {"value": r["gflops"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line))
@@ -248,8 +276,23 @@ class Runner:
                 else m.run_segment_hybrid_plan(self.plan, self.ci, self.va, B))
 
 
+def local_ms(torch, fn, warm, iters):
+    """Mean device time of one call on this rank: CUDA events around back-to-back calls."""
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
 def timed_loop(torch, fn, steps, dist_on):
-    """K back-to-back calls between two CUDA events on the current stream."""
+    """K back-to-back calls between two CUDA events on the current stream, bracketed by a
+    barrier + synchronize on both sides; returns (max over ranks, per-rank list) in ms."""
     import torch.distributed as dist
     torch.cuda.synchronize()
     if dist_on:
@@ -264,20 +307,18 @@ def timed_loop(torch, fn, steps, dist_on):
     if dist_on:
         dist.barrier()
     ms = e0.elapsed_time(e1)
-    timed_loop.rank_ms = [ms]
+    every = [ms]
     if dist_on:
         t = torch.tensor([ms], device="cuda", dtype=torch.float64)
-        every = torch.empty(dist.get_world_size(), device="cuda", dtype=torch.float64)
-        dist.all_gather_into_tensor(every, t)
-        timed_loop.rank_ms = [float(x) for x in every.tolist()]     # per rank, for the balance report
-        ms = max(timed_loop.rank_ms)
-    return ms
+        out = torch.empty(dist.get_world_size(), device="cuda", dtype=torch.float64)
+        dist.all_gather_into_tensor(out, t)
+        every = [float(x) for x in out.tolist()]
+    return max(every), every
 
 
 def zo_phase_times(torch, runner, B, iters=20):
     """Average duration of each ZERO_OVERHEAD phase timed alone (chunks, small rows, merge)
     and of the launch that a normal run uses for the two data phases together."""
-    import ctypes as C
     from ra_spmm_b200 import _capi
     lib = _capi.load()
     Cbuf = torch.empty((runner.M, runner.N), dtype=torch.float32, device=runner.dev)
@@ -288,17 +329,158 @@ def zo_phase_times(torch, runner, B, iters=20):
         call = lambda: lib.ra_zo_plan_run_phases(runner.plan._h, runner.rp.data_ptr(), runner.ci.data_ptr(),
                                                  runner.va.data_ptr(), B.data_ptr(), Cbuf.data_ptr(),
                                                  runner.N, mask, st)
-        for _ in range(3):
-            call()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(iters):
-            call()
-        e1.record()
-        torch.cuda.synchronize()
-        out[name] = e0.elapsed_time(e1) / iters
+        out[name] = local_ms(torch, call, 3, iters)
     return out
+
+
+def resolve_kernel(cfg, selector, routed):
+    if selector == "named":
+        return CONFIG_KERNEL[cfg]
+    if selector == "routed":
+        return routed
+    return selector
+
+
+def first_row_weight(args, fam):
+    if args.row_weight is not None:
+        return args.row_weight
+    return 3.0 if fam in ("CSR_DIRECT", "ZERO_OVERHEAD_CSR") else 1.0
+
+
+def build_balanced(torch, a, kernel, K, N, dev, b_dtype, B_dev, world, rank, args, gather_times):
+    """Row blocks for `world` ranks and this rank's runner. The first cut equalises nonzeros +
+    row_weight x rows; then, `balance_rounds` times, every rank times its own block, the times
+    are exchanged (gather_times: list of all ranks' ms given this rank's ms) and the boundaries
+    move so that every block would take the same time at the measured cost per unit of weight.
+    The best cut seen is kept. Returns (bounds, runner, log of rounds)."""
+    from ra_spmm_b200 import partition as P
+    fam = kernel.replace("_TF32", "")
+    rw = first_row_weight(args, fam)
+    bounds = P.nnz_balanced_row_splits(a.rowptr, world, row_weight=rw)
+
+    def make(b):
+        return Runner(kernel, P.row_block(a.rowptr, a.colind, a.vals, int(b[rank]), int(b[rank + 1])), K, N, dev, b_dtype)
+
+    runner = make(bounds)
+    log = []
+    if world == 1 or args.balance_rounds <= 0:
+        return bounds, runner, log
+    best = None
+    for rnd in range(args.balance_rounds + 1):
+        times = gather_times(local_ms(torch, lambda: runner(B_dev), 5, 20))
+        log.append({"bounds": [int(x) for x in bounds], "ms": [round(t, 4) for t in times]})
+        if best is None or max(times) < best[0]:
+            best = (max(times), bounds.copy())
+        if rnd == args.balance_rounds or max(times) <= 1.02 * (sum(times) / len(times)):
+            break
+        bounds = P.rebalance_by_time(a.rowptr, bounds, times, row_weight=rw)
+        del runner
+        runner = make(bounds)
+    if not all(int(x) == int(y) for x, y in zip(bounds, best[1])):
+        bounds = best[1]
+        del runner
+        runner = make(bounds)
+    return bounds, runner, log
+
+
+def parity_check(torch, runner, B_dev, a, B, kernel, budget_s=3.0):
+    """Relative Frobenius error of the kernel's C against torch.sparse.mm on the host cores,
+    on a strided row sample sized to about `budget_s` of CPU time (all rows when that fits)."""
+    cpu = cpu_spmm_bench(a, B, steps=1, warmup=0, budget_s=budget_s, keep_result=True)
+    C = runner(B_dev)[:: cpu["stride"]].float().cpu()
+    ref = cpu["result"]
+    err = float(torch.linalg.vector_norm((C.double() - ref.double()).flatten()) /
+                torch.linalg.vector_norm(ref.double().flatten()))
+    tile = kernel.replace("_TF32", "") in ("TC_DIRECT", "COMMUNITY_TC", "SEGMENT_HYBRID")
+    tol = TOL["tile"] if tile else TOL["fp32"]
+    return {"rel_fro_vs_cpu_sparse_mm": err, "tolerance": tol, "ok": err < tol,
+            "rows": f"0::{cpu['stride']} ({ref.shape[0]} rows)"}, cpu
+
+
+def traffic_entry(cfg, kernel):
+    """DRAM bytes per SpMM from the committed ncu captures (profiles/dram_traffic.json)."""
+    f = ROOT / "profiles" / "dram_traffic.json"
+    try:
+        e = json.loads(f.read_text()).get(f"{cfg}:{kernel}")
+    except Exception:
+        return None, None
+    if isinstance(e, dict):
+        return e.get("bytes"), e.get("source")
+    return e, "profiles/dram_traffic.json"
+
+
+def measure_entry(torch, dist, args, cfg, selector, dev, world, rank, peak):
+    """One `also` entry: a configuration through one kernel, 50 warm-ups + 200 timed launches."""
+    from ra_spmm_b200 import ra_spmm
+    dist_on = world > 1
+    a, N, B, b_dtype = load_config(cfg, args.scale, rank, dist_on)
+    feats = ra_spmm.make_router_plan(torch.from_numpy(a.rowptr).to(dev), None, None, a.M, a.K, N)
+    routed = feats["chosen_path"] + ("_TF32" if feats["use_tf32"] else "")
+    kernel = resolve_kernel(cfg, selector, routed)
+    fam = kernel.replace("_TF32", "")
+    B_dev = B.to(dev)
+    if kernel.endswith("_TF32") or fam in ("CSR_DIRECT", "ZERO_OVERHEAD_CSR"):
+        B_dev = B_dev.float()
+
+    def gather_times(ms):
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        out = torch.empty(world, device=dev, dtype=torch.float64)
+        dist.all_gather_into_tensor(out, t)
+        return [float(x) for x in out.tolist()]
+
+    bounds, runner, _ = build_balanced(torch, a, kernel, a.K, N, dev, b_dtype, B_dev, world, rank, args, gather_times)
+    for _ in range(args.inner_warmup):
+        runner(B_dev)
+    ms_total, every = timed_loop(torch, lambda: runner(B_dev), args.inner_iters, dist_on)
+    ms = ms_total / args.inner_iters
+    sA = 2 if cfg == "C3" else 4
+    sB = 2 if B_dev.dtype == torch.float16 else 4
+    bytes_algo = algorithmic_bytes(a.M, a.K, a.nnz, N, sA, sB)
+    entry = {"config": cfg, "kernel": kernel, "selector": selector, "routed_kernel": routed,
+             "ms_per_step": ms, "gflops": 2.0 * a.nnz * N / (ms * 1e-3) / 1e9,
+             "bytes_algo": bytes_algo, "nnz": a.nnz, "N": N,
+             "roofline_frac": bytes_algo / (ms * 1e-3) / 1e9 / (peak * world),
+             "warmup": args.inner_warmup, "iters": args.inner_iters}
+    tb, src = traffic_entry(cfg, kernel)
+    if tb is not None and world == 1 and args.scale == 1.0:
+        entry["traffic"], entry["traffic_source"] = tb, src
+    if world > 1:
+        entry["rank_ms"] = [x / args.inner_iters for x in every]
+    if world == 1 and rank == 0 and not args.no_cpu_baseline:
+        entry["parity"], _ = parity_check(torch, runner, B_dev, a, B, kernel)
+    del runner, B_dev
+    torch.cuda.empty_cache()
+    return entry
+
+
+def emulate_ranks(torch, args, a, N, B, b_dtype, kernel, dev):
+    """One GPU, P row blocks timed one after the other: the balance a P-rank run would see."""
+    from ra_spmm_b200 import partition as P
+    Pn = args.emulate_ranks
+    fam = kernel.replace("_TF32", "")
+    B_dev = B.to(dev)
+    if kernel.endswith("_TF32") or fam in ("CSR_DIRECT", "ZERO_OVERHEAD_CSR"):
+        B_dev = B_dev.float()
+    rw = first_row_weight(args, fam)
+    bounds = P.nnz_balanced_row_splits(a.rowptr, Pn, row_weight=rw)
+    whole = Runner(kernel, (a.rowptr, a.colind, a.vals), a.K, N, dev, b_dtype)
+    t1 = local_ms(torch, lambda: whole(B_dev), 5, 20)
+    del whole
+    rounds = []
+    for rnd in range(args.balance_rounds + 1):
+        times = []
+        for r in range(Pn):
+            run = Runner(kernel, P.row_block(a.rowptr, a.colind, a.vals, int(bounds[r]), int(bounds[r + 1])),
+                         a.K, N, dev, b_dtype)
+            times.append(local_ms(torch, lambda: run(B_dev), 5, 20))
+            del run
+        rounds.append({"round": rnd, "max_ms": max(times), "mean_ms": sum(times) / Pn,
+                       "efficiency_vs_1gpu": t1 / (Pn * max(times)), "ms": [round(t, 4) for t in times],
+                       "rows": [int(bounds[i + 1] - bounds[i]) for i in range(Pn)],
+                       "nnz": [int(a.rowptr[int(bounds[i + 1])] - a.rowptr[int(bounds[i])]) for i in range(Pn)]})
+        if rnd < args.balance_rounds:
+            bounds = P.rebalance_by_time(a.rowptr, bounds, times, row_weight=rw)
+    print(json.dumps({"emulated_ranks": Pn, "kernel": kernel, "ms_1gpu": t1, "rounds": rounds}))
 
 
 def main():
@@ -309,7 +491,6 @@ def main():
     import numpy as np
     import torch
     import torch.distributed as dist
-    from ra_spmm_b200 import partition as P
     from ra_spmm_b200 import ra_spmm
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -324,44 +505,33 @@ def main():
             os.environ["NCCL_DEBUG"] = "WARN"      # keep stdout to the one JSON line
         dist.init_process_group("nccl", device_id=dev)
     n_gpus = world
+    peak, peak_kind = measured_peak()
 
-    a, N, B, b_dtype = load_config(args.config, args.scale)
+    a, N, B, b_dtype = load_config(args.config, args.scale, rank, dist_on)
     M, K, nnz = a.M, a.K, a.nnz
 
     # routing decision on the global matrix (device feature scan)
     feats = ra_spmm.make_router_plan(torch.from_numpy(a.rowptr).to(dev), None, None, M, K, N)
     routed = feats["chosen_path"] + ("_TF32" if feats["use_tf32"] else "")
-    if args.kernel == "named":
-        kernel = CONFIG_KERNEL[args.config]          # the kernel BASELINE.json names for this configuration
-    elif args.kernel == "routed":
-        kernel = routed
-    else:
-        kernel = args.kernel
-
-    # rank grid: row blocks of A x column panels of B (panels only when B exceeds the L2)
+    kernel = resolve_kernel(args.config, args.kernel, routed)
+    if args.emulate_ranks > 1:
+        return emulate_ranks(torch, args, a, N, B, b_dtype, kernel, dev)
     fam0 = kernel.replace("_TF32", "")
-    sB_bytes = 2 if b_dtype == "float16" else 4
-    if args.shard == "rows":
-        grid_rows, grid_cols = world, 1
-    else:
-        grid_rows, grid_cols = P.choose_grid(world, N, K, sB_bytes,
-                                             column_shard=fam0 in ("CSR_DIRECT", "ZERO_OVERHEAD_CSR"))
-    row_id, col_id = rank // grid_cols, rank % grid_cols
-    Nl = N // grid_cols
-    row_weight = args.row_weight if args.row_weight is not None else \
-        (3.0 if fam0 in ("CSR_DIRECT", "ZERO_OVERHEAD_CSR") else 1.0)
-    bounds = P.nnz_balanced_row_splits(a.rowptr, grid_rows, row_weight=row_weight)
-    r0, r1 = int(bounds[row_id]), int(bounds[row_id + 1])
-    local = P.row_block(a.rowptr, a.colind, a.vals, r0, r1)
-    runner = Runner(kernel, local, K, Nl, dev, b_dtype)
-
-    B = B[:, col_id * Nl:(col_id + 1) * Nl].contiguous()
-    B_host = B.contiguous().pin_memory()
-    B_dev = B_host.to(dev, non_blocking=True)
-    if runner.tf32 or runner.fam in ("CSR_DIRECT", "ZERO_OVERHEAD_CSR"):
-        B_dev = B_dev.float()
-        B_host = B_host.float().contiguous().pin_memory()
+    f32_operand = kernel.endswith("_TF32") or fam0 in ("CSR_DIRECT", "ZERO_OVERHEAD_CSR")
+    if f32_operand:
+        B = B.float()
+    B_dev = B.to(dev)
     torch.cuda.synchronize()
+
+    def gather_times(ms):
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        out = torch.empty(world, device=dev, dtype=torch.float64)
+        dist.all_gather_into_tensor(out, t)
+        return [float(x) for x in out.tolist()]
+
+    bounds, runner, balance_log = build_balanced(torch, a, kernel, K, N, dev, b_dtype, B_dev, world, rank,
+                                                 args, gather_times)
+    r0, r1 = int(bounds[rank]), int(bounds[rank + 1])
 
     # ---- device-resident timing ------------------------------------------------
     for _ in range(max(args.warmup, 3)):
@@ -369,18 +539,25 @@ def main():
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    ms_total = timed_loop(torch, lambda: runner(B_dev), args.steps, dist_on)
+    ms_total, rank_ms = timed_loop(torch, lambda: runner(B_dev), args.steps, dist_on)
     clocks = sampler.stop() if rank == 0 else None
     ms_step = ms_total / args.steps
-    rank_ms_step = [x / args.steps for x in timed_loop.rank_ms]
+    rank_ms_step = [x / args.steps for x in rank_ms]
     gflops = 2.0 * nnz * N / (ms_step * 1e-3) / 1e9
 
-    # ---- end to end: pinned host B in, C out, every step --------------------------
-    # Three streams (copy-in, compute, copy-out) with two staging buffers, so the
-    # H2D of step i+1 and the D2H of step i-1 overlap the SpMM of step i; every
-    # step still moves its own B in and its own C out.
-    C_host = [torch.empty((r1 - r0, Nl), dtype=torch.float32).pin_memory() for _ in range(2)]
-    B_stage = [torch.empty_like(B_dev) for _ in range(2)]
+    # ---- end to end: host B in, C out, every step ---------------------------------
+    # Every rank owns rows [rank*Ks, (rank+1)*Ks) of B in pinned host memory. Per step it
+    # uploads that slab, one NCCL all-gather rebuilds the replica of B on every GPU (the SpMM
+    # reads its own GPU's memory only), the SpMM runs, and the rank's slab of C goes back to
+    # pinned host memory. Three streams (copy-in + gather, compute, copy-out) and two staging
+    # buffers, so the upload of step i+1 and the download of step i-1 overlap the SpMM of step i.
+    Ks = (K + world - 1) // world
+    slab_rows = max(0, min(K, (rank + 1) * Ks) - rank * Ks)
+    slab_host = torch.zeros((Ks, N), dtype=B.dtype).pin_memory()
+    slab_host[:slab_rows].copy_(B[rank * Ks: rank * Ks + slab_rows])
+    C_host = [torch.empty((r1 - r0, N), dtype=torch.float32).pin_memory() for _ in range(2)]
+    B_stage = [torch.empty((world * Ks, N), dtype=B.dtype, device=dev) for _ in range(2)]
+    slab_dev = [torch.empty((Ks, N), dtype=B.dtype, device=dev) for _ in range(2)] if dist_on else None
     s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
     s_main = torch.cuda.current_stream()
 
@@ -394,10 +571,14 @@ def main():
             with torch.cuda.stream(s_in):
                 if ev_done[k] is not None:
                     s_in.wait_event(ev_done[k])
-                B_stage[k].copy_(B_host, non_blocking=True)
+                if dist_on:
+                    slab_dev[k].copy_(slab_host, non_blocking=True)
+                    dist.all_gather_into_tensor(B_stage[k], slab_dev[k])
+                else:
+                    B_stage[k].copy_(slab_host, non_blocking=True)
                 ev_in[k].record(s_in)
             s_main.wait_event(ev_in[k])
-            Cd = runner(B_stage[k])
+            Cd = runner(B_stage[k][:K])
             ev_done[k] = torch.cuda.Event(); ev_done[k].record(s_main)
             with torch.cuda.stream(s_out):
                 s_out.wait_event(ev_done[k])
@@ -414,26 +595,25 @@ def main():
 
     e2e_run(2)
     e2e_steps = max(1, min(args.steps, args.e2e_steps))
-    ms_e2e = timed_loop(torch, lambda: e2e_run(e2e_steps), 1, dist_on) / e2e_steps
+    ms_e2e = timed_loop(torch, lambda: e2e_run(e2e_steps), 1, dist_on)[0] / e2e_steps
     e2e_gflops = 2.0 * nnz * N / (ms_e2e * 1e-3) / 1e9
+    h2d_bytes = int(slab_host.numel() * slab_host.element_size()) * n_gpus
+    del B_stage, slab_dev
+    torch.cuda.empty_cache()
 
+    line = None
     if rank == 0:
-        peak, peak_kind = measured_peak()
         sA = 2 if args.config == "C3" else 4
-        sB = 2 if b_dtype == "float16" else 4
+        sB = 2 if B.dtype == torch.float16 else 4
         bytes_algo = algorithmic_bytes(M, K, nnz, N, sA, sB)
         achieved = bytes_algo / (ms_step * 1e-3) / 1e9
         roof = {"bound": "hbm", "achieved": achieved, "peak": peak * n_gpus, "unit": "GB/s",
                 "frac": achieved / (peak * n_gpus), "peak_source": f"of {peak_kind}",
-                "bytes_algo_per_step": bytes_algo, "traffic": None,
+                "bytes_algo_per_step": bytes_algo, "traffic": None, "traffic_source": None,
                 "launch": f"one {kernel} SpMM = {runner.launches} kernel launch(es); duration = CUDA-event "
                           f"time of the step"}
-        traffic_file = ROOT / "profiles" / "dram_traffic.json"
-        if traffic_file.exists() and args.scale == 1.0 and n_gpus == 1:     # captured at full size on one GPU
-            try:
-                roof["traffic"] = json.loads(traffic_file.read_text()).get(f"{args.config}:{kernel}")
-            except Exception:
-                pass
+        if args.scale == 1.0 and n_gpus == 1:     # captures are of one GPU at full size (or scaled to it)
+            roof["traffic"], roof["traffic_source"] = traffic_entry(args.config, kernel)
         if runner.fam == "ZERO_OVERHEAD_CSR" and n_gpus == 1:
             ph = zo_phase_times(torch, runner, B_dev)
             fused = "csr_stream_kernel<chunks + small rows, one launch>"
@@ -443,6 +623,7 @@ def main():
             # share = part of a step's launches; phases not launched on their own in a step have none
             roof["kernels"] = {k: {"ms": v, "share": (v / tot) if k in used else None} for k, v in ph.items()}
             roof["dominant_kernel"] = max(used, key=lambda k: ph[k])
+        row_weight = first_row_weight(args, fam0)
         line = {
             "metric": METRIC, "value": gflops, "unit": UNIT, "n_gpus": n_gpus, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
@@ -452,26 +633,56 @@ def main():
                        "routed_kernel": routed, "M": M, "K": K, "nnz": nnz, "N": N,
                        "avg_degree": feats["feature_values"]["avg_nnz_per_row"],
                        "degree_cv": feats["feature_values"]["degree_cv"],
-                       "partition": f"{grid_rows} row block(s) of equal weight (nnz + {row_weight:g} x rows) x {grid_cols} "
-                                    f"column panel(s) of B ({Nl} columns per rank), no collective",
+                       "partition": f"{n_gpus} contiguous row block(s), first cut by nnz + {row_weight:g} x rows, "
+                                    f"then tuned from the measured time of each rank's block; B replicated, "
+                                    f"no collective in the device-timed SpMM",
                        "l2": f"inputs larger than L2: B {sB * K * N / 1e6:.0f} MB + C {4 * M * N / 1e6:.0f} MB per step",
                        "a_resident": "CSR arrays and the plan are uploaded/built once (warm protocol)"},
             "roofline": roof, "clocks": clocks,
             "e2e": {"value": e2e_gflops, "unit": UNIT, "ms_per_step": ms_e2e,
-                    "h2d_bytes_per_step": int(B_host.numel() * B_host.element_size()) * n_gpus,
-                    "d2h_bytes_per_step": int(4 * M * N), "steps": e2e_steps},
+                    "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": int(4 * M * N), "steps": e2e_steps,
+                    "path": ("pinned K/P-row slab of B per rank -> NCCL all-gather of the replica -> SpMM -> "
+                             "rank's slab of C to pinned host memory") if dist_on else
+                            "pinned B -> device, SpMM, C -> pinned host memory"},
             "gpu_launches": runner.launches * args.steps * n_gpus,
             "edgewise_gbs": (4 * (M + 1) + (4 + sA) * nnz + sB * nnz * N + 4 * M * N) / (ms_step * 1e-3) / 1e9,
         }
         if n_gpus > 1:
             # balance report: per-rank step time and the nonzeros / rows of each row block
             line["ranks"] = {"ms_per_step": rank_ms_step,
-                             "nnz": [int(a.rowptr[int(bounds[i + 1])] - a.rowptr[int(bounds[i])]) for i in range(grid_rows)],
-                             "rows": [int(bounds[i + 1] - bounds[i]) for i in range(grid_rows)]}
+                             "nnz": [int(a.rowptr[int(bounds[i + 1])] - a.rowptr[int(bounds[i])]) for i in range(n_gpus)],
+                             "rows": [int(bounds[i + 1] - bounds[i]) for i in range(n_gpus)],
+                             "balance_rounds": balance_log}
         if n_gpus == 1 and not args.no_cpu_baseline:
-            v, ms_cpu, cores, sample = cpu_spmm_bench(a, B, steps=5, warmup=1, budget_s=20.0)
-            line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cores, "kind": "reference",
-                                    "sample": sample, "ms_per_pass": ms_cpu}
+            cpu = cpu_spmm_bench(a, B, steps=5, warmup=1, budget_s=20.0, keep_result=True)
+            line["cpu_baseline"] = {"value": cpu["gflops"], "unit": UNIT, "cores": cpu["cores"], "kind": "reference",
+                                    "sample": cpu["sample"], "ms_per_pass": cpu["ms"]}
+            # parity of the timed kernel against that leg's own product (outside every timed region)
+            C = runner(B_dev)[:: cpu["stride"]].float().cpu()
+            ref = cpu.pop("result")
+            err = float(torch.linalg.vector_norm((C.double() - ref.double()).flatten()) /
+                        torch.linalg.vector_norm(ref.double().flatten()))
+            tol = TOL["tile"] if fam0 in ("TC_DIRECT", "COMMUNITY_TC", "SEGMENT_HYBRID") else TOL["fp32"]
+            line["parity"] = {"rel_fro_vs_cpu_sparse_mm": err, "tolerance": tol, "ok": err < tol,
+                              "rows": f"0::{cpu['stride']} ({ref.shape[0]} rows)"}
+            del C, ref
+    del runner, B_dev
+    torch.cuda.empty_cache()
+
+    # ---- the other configurations / kernels, same protocol, same run -------------------
+    want_also = args.also == "on" or (args.also == "auto" and args.config == DEFAULT_CONFIG
+                                      and args.kernel == "named" and args.scale == 1.0)
+    if want_also:
+        also = []
+        for cfg, sel in ALSO:
+            try:
+                also.append(measure_entry(torch, dist, args, cfg, sel, dev, world, rank, peak))
+            except Exception as exc:                # one entry failing must not lose the headline
+                also.append({"config": cfg, "selector": sel, "error": f"{type(exc).__name__}: {exc}"})
+        if rank == 0:
+            line["also"] = also
+            line["gpu_launches"] += sum(e.get("iters", 0) for e in also) * n_gpus
+    if rank == 0:
         print(json.dumps(line))
     if dist_on:
         dist.barrier()

@@ -131,6 +131,22 @@ RA_API int ra_features_from_rowptr_device(const int32_t* d_rowptr, int M, int K,
  * (router/router_dispatch.cpp:107-464, 979-1110) for the MAIN portfolio. */
 RA_API int ra_route(const RaFeatures* features, int portfolio, RaRoute* out);
 
+/* Diagnostic half of the decision dict: compute_router_scores (router/router_scores.cpp:27-86)
+ * and the per-path rejection code / text that compute_feasible and the legacy selection stage
+ * of route_dispatch leave behind (router/router_dispatch.cpp:107-464, 668-966), as plan_to_dict
+ * publishes them (bindings/ra_bindings.cpp:650-716). MAIN portfolio only. `route` is the result
+ * of ra_route for the same features. */
+typedef struct RaRouteDetails {
+    float   scores[8];   /* csr_direct, csr_adaptive, staged_reuse, tc_sparse, row_split_cuda,
+                            tc_reordered, hybrid_tc_cuda, cusparse                           */
+    int32_t rejection_code[RA_PATH_COUNT];          /* RejectReason, ra_common.h:146-160     */
+    char    rejection_detail[RA_PATH_COUNT][128];   /* NUL-terminated                        */
+    float   gate_margin_raw, gate_margin_norm;
+} RaRouteDetails;
+RA_API int ra_route_details(const RaFeatures* features, int portfolio, const RaRoute* route,
+                            RaRouteDetails* out);
+RA_API const char* ra_reject_reason_name(int code);   /* reject_reason_str, ra_common.h:162-179 */
+
 /* ---- CSR_DIRECT --------------------------------------------------------
  * Replaces csr_direct_spmm (csr/csr_direct.cu:234-338). C is fully overwritten
  * (empty rows become zero rows). */

@@ -146,6 +146,71 @@ def route(avg_nnz, degree_cv, M, N):
                 decision_reason=st["reason"], estimated_risk=st["risk"], feasible_by_path=feas)
 
 
+REJECT_NAMES = ["CHOSEN", "NOT_FEASIBLE", "LOW_FILL", "LOW_COVERAGE", "HIGH_SKEW", "SMALL_N",
+                "INSUFFICIENT_NNZ", "LOW_OCCUPANCY", "LOW_DEGREE_SKEW", "NOT_STRONG_ENOUGH",
+                "MARGIN_TOO_SMALL", "NOT_IN_PORTFOLIO", "UNKNOWN"]     # reject_reason_str, ra_common.h:162-179
+SCORE_KEYS = ("csr_direct", "csr_adaptive", "staged_reuse", "tc_sparse", "row_split_cuda",
+              "tc_reordered", "hybrid_tc_cuda", "cusparse")
+
+
+def _g(x):
+    """iostream formatting of a float (operator<< with the default precision of 6)."""
+    return "%g" % float(np.float32(x))
+
+
+def route_details(avg_nnz, degree_cv, M, N):
+    """Diagnostic half of the decision dict on the MAIN portfolio (all proxies zero):
+    compute_router_scores (router/router_scores.cpp:27-86, float32 arithmetic in the
+    reference's order) and the rejection code / text per path that compute_feasible
+    (router/router_dispatch.cpp:107-464) and the legacy stage (:668-966) leave behind:
+    the stage always settles on CUSPARSE (its only feasible candidate, suitability >= 0.34),
+    which marks CSR_DIRECT "not strong enough"; the seven-rule choice is then marked CHOSEN."""
+    d, cv = f32(avg_nnz), f32(degree_cv)
+    one, zero = f32(1.0), f32(0.0)
+    unit = lambda x: min(one, max(zero, f32(x)))
+    n512 = unit(f32(N) / f32(512.0))
+    uniformity = unit(one - cv / f32(2.0))
+    row_split = unit(f32(0.20) * n512)
+    locality = unit(f32(0.15) * uniformity + f32(0.10) * n512)
+    scores = dict(
+        csr_direct=unit(f32(0.40) * uniformity + f32(0.25) * (one - row_split)
+                        + f32(0.20) * (one - locality) + f32(0.15) * (one - zero)),
+        csr_adaptive=f32(0.60) * unit(cv / f32(2.0)),
+        staged_reuse=zero,
+        tc_sparse=f32(0.20) * unit(one - cv / f32(1.8)),
+        row_split_cuda=row_split,
+        tc_reordered=unit(f32(0.65) * locality + f32(0.15) * uniformity),
+        hybrid_tc_cuda=unit(f32(0.10) * locality),
+        cusparse=unit(f32(0.40) * unit(d / f32(25.0)) + f32(0.25) * uniformity
+                      + f32(0.20) * (one - locality) + f32(0.15) * n512))
+    codes, text = {}, {}
+
+    def put(path, code, detail=""):
+        codes[path], text[path] = code, detail
+
+    for path in ("CSR_ADAPTIVE", "STAGED_REUSE", "TC_SPARSE"):
+        put(path, "NOT_IN_PORTFOLIO", f"{path} not in selected portfolio")
+    put("ROW_SPLIT_CUDA", "LOW_DEGREE_SKEW", "row_split_affinity_proxy=0 < 0.65")
+    if N < 64 and M < 150000:
+        put("TC_REORDERED", "SMALL_N", f"N={_g(N)} < 64")
+        put("HYBRID_TC_CUDA", "SMALL_N", f"N={_g(N)} < 64")
+    else:
+        put("TC_REORDERED", "NOT_STRONG_ENOUGH",
+            "TC_REORDERED requires either compact reorder locality or strong scramble-recovery evidence")
+        put("HYBRID_TC_CUDA", "NOT_STRONG_ENOUGH", "mixedness_proxy=0 < 0.55")
+    for path in ("TC_DIRECT", "COMMUNITY_TC", "LOCALITY_TILED", "SEGMENT_HYBRID"):
+        put(path, *(("MARGIN_TOO_SMALL", f"N={_g(N)} < 16") if N < 16 else ("CHOSEN",)))
+    put("RODE_ENHANCED", *(("NOT_STRONG_ENOUGH", f"degree_cv={_g(cv)} < 0.8") if cv < f32(0.80) else ("CHOSEN",)))
+    put("VECTORIZED_COARSE", *(("NOT_STRONG_ENOUGH", f"avg_nnz={_g(d)} > 12") if d > f32(12.0) else ("CHOSEN",)))
+    put("ZERO_OVERHEAD_CSR", "CHOSEN")
+    put("CUSPARSE", "CHOSEN")
+    put("CSR_DIRECT", "NOT_STRONG_ENOUGH",
+        "specialized path has materially stronger regime evidence than explicit DIRECT suitability")
+    put(route(avg_nnz, degree_cv, M, N)["chosen_path"], "CHOSEN")
+    return dict(scores=scores, rejection_codes=codes, rejection_details=text,
+                gate_margin_raw=zero, gate_margin_norm=zero)
+
+
 def route_label(r):
     """Kernel label as the reference harness prints it: family + _TF32
     (ra_router_parity_test.py:88-103)."""
@@ -191,11 +256,24 @@ def zero_overhead_plan(rowptr, M):
 # ---------------------------------------------------------------------------
 # Tile format (8-row windows, 8x1 vectors, 8-vector blocks)
 # ---------------------------------------------------------------------------
-def float_to_half_bits(v):
-    """host_float_to_half_bits, tc/ra_tc_direct.cu:45-69 (round to nearest even,
-    overflow to inf, flush below 2^-25) == IEEE conversion for non-NaN input."""
-    with np.errstate(over="ignore"):
-        return np.asarray(v, dtype=np.float32).astype(np.float16).view(np.uint16)
+def float_to_half_bits(v, nan_to_inf=True):
+    """fp32 -> fp16 bits, round to nearest even, overflow to inf, flush below 2^-25.
+    nan_to_inf=True: host_float_to_half_bits of TC_DIRECT (tc/ra_tc_direct.cu:45-69), which
+    sends every all-ones exponent - NaN included - to the infinity of its sign.
+    nan_to_inf=False: float_to_half_bits of COMMUNITY_TC / SEGMENT_HYBRID
+    (tc/ra_community_tc.cu:35-38, tc/ra_segment_hybrid.cu:34-37) = __float2half_rn on the
+    host, whose NaN is the canonical 0x7FFF. The two agree on every other input."""
+    v = np.asarray(v, dtype=np.float32)
+    with np.errstate(over="ignore", invalid="ignore"):
+        out = v.astype(np.float16).view(np.uint16).copy()
+    nan = np.isnan(v)
+    if nan.any():
+        if nan_to_inf:
+            sign = ((v.view(np.uint32) >> 16) & 0x8000).astype(np.uint16)
+            out = np.where(nan, sign | np.uint16(0x7C00), out).astype(np.uint16)
+        else:
+            out = np.where(nan, np.uint16(0x7FFF), out).astype(np.uint16)
+    return out
 
 
 def community_order(rowptr, colind, M):
@@ -213,16 +291,20 @@ def community_order(rowptr, colind, M):
     return win_rows
 
 
-def tile_plan(rowptr, colind, vals, M, K, N, win_rows=None):
+def tile_plan(rowptr, colind, vals, M, K, N, win_rows=None, nan_to_inf=None):
     """build_ra_tc_direct_plan_impl, tc/ra_tc_direct.cu:627-780 (natural order),
     or the COMMUNITY_TC variant tc/ra_community_tc.cu:355-433 when `win_rows`
     is given. Returns block_offsets [W+1], atox [8*blocks], vals_f16
     [64*blocks] (uint16 bits, fragment order: index(block, vector k, row r) =
     block*64 + (r*4 + k//2)*2 + (k&1), tc/ra_tc_direct.cu:13), or None when the
-    plan is inactive (N < 16 or nnz == 0)."""
+    plan is inactive (N < 16 or nnz == 0). `nan_to_inf` picks the value conversion (see
+    float_to_half_bits); default: TC_DIRECT's for natural order, COMMUNITY_TC's with `win_rows`;
+    pass False for SEGMENT_HYBRID."""
     rowptr = np.asarray(rowptr).astype(np.int64)
     colind = np.asarray(colind).astype(np.int64)
     vals = np.asarray(vals, dtype=np.float32)
+    if nan_to_inf is None:
+        nan_to_inf = win_rows is None
     if M <= 0 or K <= 0 or N < 16 or rowptr[M] <= 0:
         return None
     W = (M + 7) // 8
@@ -256,7 +338,7 @@ def tile_plan(rowptr, colind, vals, M, K, N, win_rows=None):
     blk = block_offsets[w] + (v_in_w >> 3)
     k = v_in_w & 7
     out = np.zeros(total_blocks * 64, dtype=np.uint16)
-    out[blk * 64 + (slot * 4 + (k >> 1)) * 2 + (k & 1)] = float_to_half_bits(val)
+    out[blk * 64 + (slot * 4 + (k >> 1)) * 2 + (k & 1)] = float_to_half_bits(val, nan_to_inf)
     # zero-compressed form of the same values (the zc=true branch, tc/ra_tc_direct.cu:686-735):
     # per block a mask with bit k*8+r per stored (vector k, row r), the index of the block's
     # first stored value (a window's values start at rowptr[8w]), and the stored halves in
@@ -268,7 +350,7 @@ def tile_plan(rowptr, colind, vals, M, K, N, win_rows=None):
     val_base = np.zeros(total_blocks, dtype=np.int32)
     val_base[blk[first_of_block]] = np.flatnonzero(first_of_block).astype(np.int32)
     return dict(block_offsets=block_offsets.astype(np.int32), atox=atox, vals_f16=out,
-                val_masks=val_masks, val_base=val_base, vals_zc=float_to_half_bits(val),
+                val_masks=val_masks, val_base=val_base, vals_zc=float_to_half_bits(val, True),
                 num_windows=W, num_blocks=total_blocks, nnz=int(rowptr[M]))
 
 

@@ -43,6 +43,12 @@ class RefTileInfo(C.Structure):
                [(n, C.c_void_p) for n in ("d_val_masks", "d_val_base", "d_vals_zc")]
 
 
+class RefRouteDetails(C.Structure):
+    _fields_ = [("scores", C.c_float * 8), ("rejection_code", C.c_int * PATH_COUNT),
+                ("rejection_detail", (C.c_char * 128) * PATH_COUNT),
+                ("gate_margin_raw", C.c_float), ("gate_margin_norm", C.c_float)]
+
+
 _cache = {}
 
 
@@ -61,8 +67,17 @@ def router():
         lib.ref_route_from_rowptr.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.POINTER(RefRoute)]
         lib.ref_route_from_features.argtypes = [C.c_float, C.c_float, C.c_float, C.c_int, C.c_int,
                                                 C.c_int, C.c_int, C.POINTER(RefRoute)]
+        if hasattr(lib, "ref_route_details_from_features"):
+            lib.ref_route_details_from_features.argtypes = [C.c_float, C.c_float, C.c_float, C.c_int, C.c_int,
+                                                            C.c_int, C.c_int, C.POINTER(RefRouteDetails)]
         lib._typed = True
     return lib
+
+
+def ref_route_details_from_features(avg, std, cv, M, K, N, nnz) -> RefRouteDetails:
+    out = RefRouteDetails()
+    router().ref_route_details_from_features(float(avg), float(std), float(cv), M, K, N, nnz, C.byref(out))
+    return out
 
 
 def ref_route_from_rowptr(rowptr: np.ndarray, M, K, N) -> RefRoute:

@@ -49,4 +49,34 @@ int ref_route_from_features(float avg, float stddev, float cv, int M, int K, int
     return 0;
 }
 
+// scores, rejection codes / texts and gate margins of the reference decision (the values that
+// plan_to_dict publishes, bindings/ra_bindings.cpp:650-716) for given production features
+struct RefRouteDetails {
+    float scores[8];
+    int   rejection_code[NEXT_PATH_COUNT];
+    char  rejection_detail[NEXT_PATH_COUNT][128];
+    float gate_margin_raw, gate_margin_norm;
+};
+
+int ref_route_details_from_features(float avg, float stddev, float cv, int M, int K, int N, int nnz,
+                                    RefRouteDetails* out) {
+    RouterFeatures f{};
+    f.avg_nnz_per_row = avg; f.std_nnz_per_row = stddev; f.degree_cv = cv;
+    f.matrix_M = M; f.matrix_K = K; f.output_dim_N = N; f.total_nnz = nnz;
+    const RouterScores sc = compute_router_scores(f);
+    RouterPlan plan = route_dispatch(f, sc, Portfolio::MAIN);
+    std::memset(out, 0, sizeof(*out));
+    const float s[8] = {plan.scores.csr_direct_score, plan.scores.csr_adaptive_score, plan.scores.staged_reuse_score,
+                        plan.scores.tc_sparse_score, plan.scores.row_split_cuda_score, plan.scores.tc_reordered_score,
+                        plan.scores.hybrid_tc_cuda_score, plan.scores.cusparse_score};
+    for (int i = 0; i < 8; ++i) out->scores[i] = s[i];
+    for (int i = 0; i < NEXT_PATH_COUNT; ++i) {
+        out->rejection_code[i] = static_cast<int>(plan.rejection_code[i]);
+        std::strncpy(out->rejection_detail[i], plan.rejection_detail[i].c_str(), sizeof(out->rejection_detail[i]) - 1);
+    }
+    out->gate_margin_raw = plan.gate_margin_raw;
+    out->gate_margin_norm = plan.gate_margin_norm;
+    return 0;
+}
+
 }  // extern "C"

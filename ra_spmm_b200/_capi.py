@@ -27,6 +27,7 @@ DTYPE_F32, DTYPE_F16 = 0, 1
 EXPORTED_SYMBOLS = [
     "ra_last_error_string", "ra_path_name", "ra_version", "ra_copy_to_host", "ra_fnv1a64_host",
     "ra_features_from_rowptr_host", "ra_features_from_rowptr_device", "ra_route",
+    "ra_route_details", "ra_reject_reason_name",
     "ra_csr_direct_spmm",
     "ra_zo_plan_create", "ra_zo_plan_info", "ra_zo_plan_run", "ra_zo_plan_destroy",
     "ra_zo_plan_run_phases", "ra_zo_plan_run_noalloc",
@@ -47,6 +48,18 @@ class RaRoute(C.Structure):
     _fields_ = [
         ("chosen_path", C.c_int32), ("use_tf32", C.c_int32), ("estimated_risk", C.c_float),
         ("feasible", C.c_uint8 * PATH_COUNT), ("decision_reason", C.c_char * 64),
+    ]
+
+
+SCORE_KEYS = ("csr_direct", "csr_adaptive", "staged_reuse", "tc_sparse", "row_split_cuda",
+              "tc_reordered", "hybrid_tc_cuda", "cusparse")
+
+
+class RaRouteDetails(C.Structure):
+    _fields_ = [
+        ("scores", C.c_float * 8), ("rejection_code", C.c_int32 * PATH_COUNT),
+        ("rejection_detail", (C.c_char * 128) * PATH_COUNT),
+        ("gate_margin_raw", C.c_float), ("gate_margin_norm", C.c_float),
     ]
 
 
@@ -109,6 +122,9 @@ def load() -> C.CDLL:
     lib.ra_features_from_rowptr_host.argtypes = [vp, i32, i32, i32, C.POINTER(RaFeatures)]
     lib.ra_features_from_rowptr_device.argtypes = [vp, i32, i32, i32, vp, C.POINTER(RaFeatures)]
     lib.ra_route.argtypes = [C.POINTER(RaFeatures), i32, C.POINTER(RaRoute)]
+    lib.ra_route_details.argtypes = [C.POINTER(RaFeatures), i32, C.POINTER(RaRoute), C.POINTER(RaRouteDetails)]
+    lib.ra_reject_reason_name.argtypes = [i32]
+    lib.ra_reject_reason_name.restype = C.c_char_p
     lib.ra_csr_direct_spmm.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i64, vp]
     lib.ra_zo_plan_create.argtypes = [vp, i32, i32, i32, vp, C.POINTER(vp)]
     lib.ra_zo_plan_info.argtypes = [vp, C.POINTER(RaZoInfo)]

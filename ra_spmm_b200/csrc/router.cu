@@ -9,7 +9,10 @@
 // reference does; the build-time gate is evaluated in double.
 #include "common.cuh"
 
+#include <algorithm>
 #include <cstring>
+#include <sstream>
+#include <string>
 
 namespace ra {
 
@@ -152,5 +155,117 @@ extern "C" int ra_route(const RaFeatures* f, int portfolio, RaRoute* out)
     out->use_tf32 = (is_tile && tf32) ? 1 : 0;
     out->estimated_risk = risk;
     std::strncpy(out->decision_reason, reason, sizeof(out->decision_reason) - 1);
+    return RA_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Diagnostic part of the decision dict: scores and per-path rejection code / text.
+//
+// In the reference these come from compute_router_scores (router/router_scores.cpp:27-86),
+// from compute_feasible (router/router_dispatch.cpp:107-464) and from the bookkeeping of the
+// legacy selection stage (:668-966) that runs before the seven rules. On the MAIN portfolio
+// the 27 diagnostic proxies of the feature struct are zero, which fixes that stage's outcome:
+//   * ROW_SPLIT_CUDA, TC_REORDERED and HYBRID_TC_CUDA fail their first proxy threshold (or
+//     the N >= 64 gate of the latter two on matrices under 150,000 rows);
+//   * CUSPARSE is the only feasible legacy candidate and its suitability is at least 0.34,
+//     above its 0.20 floor, so the stage always settles on it, which leaves CSR_DIRECT with
+//     "not strong enough" unless the seven rules pick CSR_DIRECT afterwards;
+//   * every other feasible path keeps the code its feasibility check wrote (CHOSEN), and the
+//     seven-rule choice is marked CHOSEN with margins of zero.
+// The scores keep the reference's float32 expression order with the zero terms dropped
+// (adding an exact zero does not change a float).
+// ---------------------------------------------------------------------------
+namespace ra {
+namespace {
+
+enum RejectCode {      // values of RejectReason, ra_common.h:146-160
+    RJ_CHOSEN = 0, RJ_NOT_FEASIBLE, RJ_LOW_FILL, RJ_LOW_COVERAGE, RJ_HIGH_SKEW, RJ_SMALL_N,
+    RJ_INSUFFICIENT_NNZ, RJ_LOW_OCCUPANCY, RJ_LOW_DEGREE_SKEW, RJ_NOT_STRONG_ENOUGH,
+    RJ_MARGIN_TOO_SMALL, RJ_NOT_IN_PORTFOLIO, RJ_UNKNOWN
+};
+const char* const kRejectNames[] = {
+    "CHOSEN", "NOT_FEASIBLE", "LOW_FILL", "LOW_COVERAGE", "HIGH_SKEW", "SMALL_N", "INSUFFICIENT_NNZ",
+    "LOW_OCCUPANCY", "LOW_DEGREE_SKEW", "NOT_STRONG_ENOUGH", "MARGIN_TOO_SMALL", "NOT_IN_PORTFOLIO",
+    "UNKNOWN"};
+
+inline float unit(float x) { return std::max(0.f, std::min(1.f, x)); }
+
+// "<name>=<value> <op> <threshold>" with iostream float formatting (6 significant digits)
+std::string threshold_text(const char* name, float value, const char* op, float threshold) {
+    std::ostringstream o;
+    o << name << "=" << value << " " << op << " " << threshold;
+    return o.str();
+}
+
+void put(RaRouteDetails* out, int path, int code, const std::string& text) {
+    out->rejection_code[path] = code;
+    std::strncpy(out->rejection_detail[path], text.c_str(), sizeof(out->rejection_detail[path]) - 1);
+}
+
+}  // namespace
+}  // namespace ra
+
+extern "C" const char* ra_reject_reason_name(int code) {
+    return (code >= 0 && code <= ra::RJ_UNKNOWN) ? ra::kRejectNames[code] : "UNKNOWN";
+}
+
+extern "C" int ra_route_details(const RaFeatures* f, int portfolio, const RaRoute* route, RaRouteDetails* out)
+{
+    using namespace ra;
+    RA_REQUIRE(f && route && out, RA_ERR_INVALID_ARG, "ra_route_details: null argument");
+    RA_REQUIRE(portfolio == RA_PORTFOLIO_MAIN, RA_ERR_UNSUPPORTED,
+               "ra_route_details: only the MAIN portfolio is implemented");
+    std::memset(out, 0, sizeof(*out));
+    const float d = f->avg_nnz_per_row, cv = f->degree_cv;
+    const int N = f->output_dim_N, M = f->matrix_M;
+    const float n512 = unit(static_cast<float>(N) / 512.f);
+
+    // ---- scores ----
+    const float uniformity = unit(1.f - cv / 2.0f);
+    const float row_split_signal = unit(0.20f * n512);
+    const float locality_signal = unit(0.15f * uniformity + 0.10f * n512);
+    out->scores[0] = unit(0.40f * uniformity + 0.25f * (1.f - row_split_signal) +
+                          0.20f * (1.f - locality_signal) + 0.15f * (1.f - 0.f));          // csr_direct
+    out->scores[1] = 0.60f * unit(cv / 2.0f);                                             // csr_adaptive
+    out->scores[2] = 0.f;                                                                  // staged_reuse
+    out->scores[3] = 0.20f * unit(1.f - cv / 1.8f);                                       // tc_sparse
+    out->scores[4] = row_split_signal;                                                     // row_split_cuda
+    out->scores[5] = unit(0.65f * locality_signal + 0.15f * uniformity);                  // tc_reordered
+    out->scores[6] = unit(0.10f * locality_signal);                                       // hybrid_tc_cuda
+    out->scores[7] = unit(0.40f * unit(d / 25.f) + 0.25f * uniformity +
+                          0.20f * (1.f - locality_signal) + 0.15f * n512);                 // cusparse
+
+    // ---- feasibility bookkeeping ----
+    const bool small_n_gate = N < 64 && M < 150000;
+    const std::string n_lt_64 = threshold_text("N", static_cast<float>(N), "<", 64.f);
+    const std::string n_lt_16 = threshold_text("N", static_cast<float>(N), "<", 16.f);
+    for (int path : {RA_PATH_CSR_ADAPTIVE, RA_PATH_STAGED_REUSE, RA_PATH_TC_SPARSE})
+        put(out, path, RJ_NOT_IN_PORTFOLIO, std::string(kPathNames[path]) + " not in selected portfolio");
+    put(out, RA_PATH_ROW_SPLIT_CUDA, RJ_LOW_DEGREE_SKEW, threshold_text("row_split_affinity_proxy", 0.f, "<", 0.65f));
+    if (small_n_gate) {
+        put(out, RA_PATH_TC_REORDERED, RJ_SMALL_N, n_lt_64);
+        put(out, RA_PATH_HYBRID_TC_CUDA, RJ_SMALL_N, n_lt_64);
+    } else {
+        put(out, RA_PATH_TC_REORDERED, RJ_NOT_STRONG_ENOUGH,
+            "TC_REORDERED requires either compact reorder locality or strong scramble-recovery evidence");
+        put(out, RA_PATH_HYBRID_TC_CUDA, RJ_NOT_STRONG_ENOUGH, threshold_text("mixedness_proxy", 0.f, "<", 0.55f));
+    }
+    for (int path : {RA_PATH_TC_DIRECT, RA_PATH_COMMUNITY_TC, RA_PATH_LOCALITY_TILED, RA_PATH_SEGMENT_HYBRID}) {
+        if (N < 16) put(out, path, RJ_MARGIN_TOO_SMALL, n_lt_16);
+        else put(out, path, RJ_CHOSEN, "");
+    }
+    if (cv < 0.80f) put(out, RA_PATH_RODE_ENHANCED, RJ_NOT_STRONG_ENOUGH, threshold_text("degree_cv", cv, "<", 0.80f));
+    else put(out, RA_PATH_RODE_ENHANCED, RJ_CHOSEN, "");
+    if (d > 12.0f) put(out, RA_PATH_VECTORIZED_COARSE, RJ_NOT_STRONG_ENOUGH, threshold_text("avg_nnz", d, ">", 12.f));
+    else put(out, RA_PATH_VECTORIZED_COARSE, RJ_CHOSEN, "");
+    put(out, RA_PATH_ZERO_OVERHEAD_CSR, RJ_CHOSEN, "");
+    put(out, RA_PATH_CUSPARSE, RJ_CHOSEN, "");                 // the legacy stage's own choice
+    put(out, RA_PATH_CSR_DIRECT, RJ_NOT_STRONG_ENOUGH,
+        "specialized path has materially stronger regime evidence than explicit DIRECT suitability");
+    // the seven-rule choice (always feasible) overwrites its own entry; margins are zero
+    put(out, route->chosen_path, RJ_CHOSEN, "");
+    out->rejection_detail[route->chosen_path][0] = 0;
+    out->gate_margin_raw = 0.f;
+    out->gate_margin_norm = 0.f;
     return RA_OK;
 }

@@ -110,12 +110,23 @@ tb_window_blocks_kernel(const int* __restrict__ ws, const int* __restrict__ hsca
     }
 }
 
+// fp32 -> fp16 bits, round to nearest even. The reference converts on the host with two
+// routines that differ for NaN only: TC_DIRECT (padded and zero-compressed plans) maps every
+// value whose exponent field is all ones - NaN included - to the infinity of its sign
+// (host_float_to_half_bits, tc/ra_tc_direct.cu:45-69); COMMUNITY_TC and SEGMENT_HYBRID keep
+// the canonical NaN of __float2half_rn (tc/ra_community_tc.cu:35-38, tc/ra_segment_hybrid.cu:34-37).
+__device__ __forceinline__ uint16_t tb_half_bits(float v, int nan_to_inf)
+{
+    if (nan_to_inf && v != v) return (uint16_t)(((__float_as_uint(v) >> 16) & 0x8000u) | 0x7C00u);
+    return __half_as_ushort(__float2half_rn(v));
+}
+
 __global__ void __launch_bounds__(kTbThreads)
 tb_fill_kernel(const unsigned long long* __restrict__ keys, const unsigned* __restrict__ payload,
                const float* __restrict__ vals, const int* __restrict__ hscan,
                const int* __restrict__ ws, const int* __restrict__ block_offsets, i64 n,
                int shift_w, unsigned long long col_mask, int* __restrict__ atox,
-               uint16_t* __restrict__ vals_f16)
+               uint16_t* __restrict__ vals_f16, int nan_to_inf)
 {
     for (i64 i = (i64)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (i64)gridDim.x * blockDim.x) {
         const unsigned long long key = keys[i];
@@ -127,8 +138,7 @@ tb_fill_kernel(const unsigned long long* __restrict__ keys, const unsigned* __re
         const i64 b = (i64)block_offsets[w] + (v >> 3);
         const int k = v & 7;
         if (h1 != h0) atox[b * kVecPerBlock + k] = col;
-        const __half hv = __float2half_rn(vals[payload[i]]);
-        vals_f16[b * 64 + (slot * 4 + (k >> 1)) * 2 + (k & 1)] = __half_as_ushort(hv);
+        vals_f16[b * 64 + (slot * 4 + (k >> 1)) * 2 + (k & 1)] = tb_half_bits(vals[payload[i]], nan_to_inf);
     }
 }
 
@@ -157,7 +167,7 @@ tb_fill_zc_kernel(const unsigned long long* __restrict__ keys, const unsigned* _
             if (k == 0) val_base[b] = (int)i;            // first entry of the block
         }
         atomicOr(val_masks + b, 1ull << (k * 8 + slot));
-        vals_zc[i] = __half_as_ushort(__float2half_rn(vals[payload[i]]));
+        vals_zc[i] = tb_half_bits(vals[payload[i]], 1);
     }
 }
 
@@ -375,7 +385,8 @@ extern "C" int ra_tile_plan_create(int kind, const int32_t* rowptr, const int32_
         TB_TRY(cudaMemsetAsync(p->d_vals_f16, 0, vals_bytes, st));
         tb_fill_kernel<<<grid_for(n), kTbThreads, 0, st>>>(skeys, spay, d_vals, hs.as<int>(), wsb.as<int>(),
                                                           p->d_block_offsets, n, shift_w, col_mask,
-                                                          p->d_atox, p->d_vals_f16);
+                                                          p->d_atox, p->d_vals_f16,
+                                                          kind == RA_TILE_TC_DIRECT ? 1 : 0);
     }
     TB_TRY(cudaGetLastError());
 

@@ -1120,9 +1120,10 @@ static int launch_tile(const TileArgs& a, const void* B, bool staged, cudaStream
             }));
             RA_REQUIRE(smem_t <= 100 * 1024, RA_ERR_UNSUPPORTED, "tile SpMM: N=%d too wide for the staged kernel", a.N);
             // RA_TILE_TMA_POLL_LIMIT (tests only): polls a consumer warp spends on a stage before it
-            // gives up and reports through the status word; every other wait keeps the normal limit
+            // gives up and reports through the status word (0 = gives up at once); every other
+            // wait keeps the normal limit
             const char* poll_env = std::getenv("RA_TILE_TMA_POLL_LIMIT");
-            const int poll_limit = poll_env ? std::max(1, std::atoi(poll_env)) : kSpinLimit;
+            const int poll_limit = poll_env ? std::max(0, std::atoi(poll_env)) : kSpinLimit;
             kern_t<<<ctas_t, warps * 32, smem_t, st>>>(a, B, slices, (int)groups_t, group_bytes, status, poll_limit);
             RA_KERNEL_CHECK();
             return RA_OK;

@@ -49,40 +49,81 @@ def dense(K: int, N: int, seed: int, dtype="float32"):
     return B
 
 
-def _unique_sorted(keys: np.ndarray) -> np.ndarray:
-    """Sorted distinct keys. The sort runs on the current CUDA device when there is one
-    (seconds instead of minutes at 10^8 keys); the result is the same array either way."""
+def _cuda():
+    """The current CUDA device when torch sees one, else None. Only the sort/dedup and the
+    elementwise bit work of the generators run there (seconds instead of minutes at 10^8
+    edges); the random draws always come from numpy, so the graph is the same either way."""
     try:
         import torch
-        if torch.cuda.is_available() and keys.size >= (1 << 20):
-            t = torch.unique(torch.from_numpy(keys).cuda())
-            out = t.cpu().numpy()
-            del t
-            torch.cuda.empty_cache()
-            return out
+        return torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else None
     except (ImportError, RuntimeError):
-        pass
-    return np.unique(keys)
+        return None
 
 
-def _csr_from_keys(keys: np.ndarray, M: int, K: int):
-    """keys = row*K + col (int64), any order, duplicates allowed."""
-    keys = _unique_sorted(keys)
-    rows = keys // K
-    cols = (keys - rows * K).astype(np.int32)
-    rowptr = np.zeros(M + 1, dtype=np.int64)
-    np.cumsum(np.bincount(rows, minlength=M), out=rowptr[1:])
-    assert rowptr[-1] < 2**31
-    return rowptr.astype(np.int32), cols
+def _sorted_unique(keys: np.ndarray) -> np.ndarray:
+    """np.unique by sort + neighbour compare (numpy's hash-based unique is several times
+    slower on 10^7 integer keys)."""
+    keys = np.sort(keys, kind="stable")
+    if keys.size == 0:
+        return keys
+    keep = np.empty(keys.size, dtype=bool)
+    keep[0] = True
+    np.not_equal(keys[1:], keys[:-1], out=keep[1:])
+    return keys[keep]
 
 
-def _symmetrize_keys(u: np.ndarray, v: np.ndarray, n: int, self_loops: bool):
-    u = u.astype(np.int64); v = v.astype(np.int64)
+def _csr_from_edges(u, v, n: int, self_loops: bool):
+    """Symmetrised, deduplicated CSR structure (rowptr int32 [n+1], cols int32) of the
+    undirected edge list (u, v); `self_loops` adds the diagonal. u, v: integer numpy arrays
+    or torch tensors on the build device."""
+    dev = _cuda()
+    if dev is not None and (not isinstance(u, np.ndarray) or u.size >= (1 << 20)):
+        import torch
+        tu = (torch.from_numpy(u) if isinstance(u, np.ndarray) else u).to(dev).to(torch.int64)
+        tv = (torch.from_numpy(v) if isinstance(v, np.ndarray) else v).to(dev).to(torch.int64)
+        parts = [tu * n + tv, tv * n + tu]
+        del tu, tv
+        if self_loops:
+            d = torch.arange(n, dtype=torch.int64, device=dev)
+            parts.append(d * n + d)
+        keys = torch.unique(torch.cat(parts))
+        del parts
+        rows = torch.div(keys, n, rounding_mode="floor")
+        cols = (keys - rows * n).to(torch.int32)
+        del keys
+        rowptr = torch.zeros(n + 1, dtype=torch.int64, device=dev)
+        torch.cumsum(torch.bincount(rows, minlength=n), 0, out=rowptr[1:])
+        assert int(rowptr[-1]) < 2**31
+        out = rowptr.to(torch.int32).cpu().numpy(), cols.cpu().numpy()
+        del rows, cols, rowptr
+        torch.cuda.empty_cache()
+        return out
+    u = np.asarray(u).astype(np.int64); v = np.asarray(v).astype(np.int64)
     parts = [u * n + v, v * n + u]
     if self_loops:
         d = np.arange(n, dtype=np.int64)
         parts.append(d * n + d)
-    return np.concatenate(parts)
+    keys = _sorted_unique(np.concatenate(parts))
+    rows = keys // n
+    cols = (keys - rows * n).astype(np.int32)
+    rowptr = np.zeros(n + 1, dtype=np.int64)
+    np.cumsum(np.bincount(rows, minlength=n), out=rowptr[1:])
+    assert rowptr[-1] < 2**31
+    return rowptr.astype(np.int32), cols
+
+
+def _uniform_f32(rng, lo: float, hi: float, size: int, chunk: int = 1 << 24) -> np.ndarray:
+    """rng.uniform(lo, hi, size).astype(float32) drawn in chunks through one reused float64
+    buffer (same values: numpy's uniform is lo + (hi - lo) * next_double)."""
+    out = np.empty(size, dtype=np.float32)
+    buf = np.empty(min(chunk, max(size, 1)), dtype=np.float64)
+    for s0 in range(0, size, chunk):
+        k = min(chunk, size - s0)
+        rng.random(out=buf[:k])
+        np.multiply(buf[:k], hi - lo, out=buf[:k])
+        np.add(buf[:k], lo, out=buf[:k])
+        out[s0:s0 + k] = buf[:k]
+    return out
 
 
 # ---- C1 -----------------------------------------------------------------------
@@ -118,7 +159,7 @@ def chung_lu_power_law(n=1_048_576, gamma=2.1, mean_degree=10.0, seed=1, cap=Tru
     u = np.searchsorted(cdf, rng.random(n_edges), side="right").astype(np.int64)
     v = np.searchsorted(cdf, rng.random(n_edges), side="right").astype(np.int64)
     np.minimum(u, n - 1, out=u); np.minimum(v, n - 1, out=v)
-    rowptr, cols = _csr_from_keys(_symmetrize_keys(u, v, n, self_loops=True), n, n)
+    rowptr, cols = _csr_from_edges(u, v, n, self_loops=True)
     deg = np.diff(rowptr).astype(np.float64)
     rows = np.repeat(np.arange(n, dtype=np.int64), np.diff(rowptr))
     vals = (1.0 / np.sqrt(deg[rows] * deg[cols])).astype(np.float32)
@@ -161,7 +202,7 @@ def sbm_edges(n: int, n_comm: int, mean_degree: float, intra_frac: float, rng):
             hit = np.flatnonzero(rng.random(pairs, dtype=np.float32) < p_in)
         else:
             m = rng.binomial(pairs, p_in)
-            hit = np.unique(rng.integers(0, pairs, size=m, dtype=np.int64))
+            hit = _sorted_unique(rng.integers(0, pairs, size=m, dtype=np.int64))
         i, j = _triu_pairs(hit, sz)
         us.append(i + lo); vs.append(j + lo)
     # inter-community edges: uniform pairs, same-community pairs rejected
@@ -186,7 +227,7 @@ def sbm_graph(n=232_960, n_comm=50, mean_degree=490.0, intra_frac=0.92, seed=2,
     if shuffle:
         perm = rng.permutation(n).astype(np.int64)
         u, v = perm[u], perm[v]
-    rowptr, cols = _csr_from_keys(_symmetrize_keys(u, v, n, self_loops=False), n, n)
+    rowptr, cols = _csr_from_edges(u, v, n, self_loops=False)
     vals = rng.random(cols.size, dtype=np.float32)
     if value_dtype == "float16":
         vals = vals.astype(np.float16).astype(np.float32)
@@ -200,17 +241,40 @@ def rmat_graph(scale=22, edge_factor=16, a=0.57, b=0.19, c=0.19, seed=3) -> CSR:
     rng = np.random.default_rng(seed)
     n = 1 << scale
     m = edge_factor * n
-    u = np.zeros(m, dtype=np.int64)
-    v = np.zeros(m, dtype=np.int64)
+    assert scale <= 31
     ab, abc = a + b, a + b + c
-    for _ in range(scale):
-        r = rng.random(m, dtype=np.float32)
-        row_bit = r >= ab
-        col_bit = ((r >= a) & (r < ab)) | (r >= abc)
-        u = (u << 1) | row_bit
-        v = (v << 1) | col_bit
-    rowptr, cols = _csr_from_keys(_symmetrize_keys(u, v, n, self_loops=False), n, n)
-    vals = rng.uniform(-1.0, 1.0, size=cols.size).astype(np.float32)
+    r = np.empty(m, dtype=np.float32)
+    dev = _cuda() if m >= (1 << 20) else None
+    if dev is not None:                 # draws on the host, bit assembly on the device
+        import torch
+        u = torch.zeros(m, dtype=torch.int32, device=dev)
+        v = torch.zeros(m, dtype=torch.int32, device=dev)
+        # thresholds as float32, the type numpy compares a float32 array against a Python float in
+        a32, ab32, abc32 = (float(np.float32(x)) for x in (a, ab, abc))
+        for _ in range(scale):
+            rng.random(out=r, dtype=np.float32)
+            t = torch.from_numpy(r).to(dev)
+            u.mul_(2).add_(t >= ab32)
+            v.mul_(2).add_(((t >= a32) & (t < ab32)) | (t >= abc32))
+        del t
+    else:
+        u = np.zeros(m, dtype=np.uint32)
+        v = np.zeros(m, dtype=np.uint32)
+        t1 = np.empty(m, dtype=bool)
+        t2 = np.empty(m, dtype=bool)
+        for _ in range(scale):
+            rng.random(out=r, dtype=np.float32)
+            np.left_shift(u, 1, out=u)
+            np.bitwise_or(u, np.greater_equal(r, ab, out=t1), out=u)        # row bit
+            np.greater_equal(r, a, out=t1)
+            np.less(r, ab, out=t2)
+            t1 &= t2
+            t1 |= np.greater_equal(r, abc, out=t2)                           # column bit
+            np.left_shift(v, 1, out=v)
+            np.bitwise_or(v, t1, out=v)
+    del r
+    rowptr, cols = _csr_from_edges(u, v, n, self_loops=False)
+    vals = _uniform_f32(rng, -1.0, 1.0, cols.size)
     return CSR(n, n, rowptr, cols, vals)
 
 
@@ -222,7 +286,7 @@ def gcn_normalized_sbm(n=2_449_029, n_comm=500, mean_degree=50.0, intra_frac=0.9
     u, v = sbm_edges(n, n_comm, mean_degree, intra_frac, rng)
     perm = rng.permutation(n).astype(np.int64)
     u, v = perm[u], perm[v]
-    rowptr, cols = _csr_from_keys(_symmetrize_keys(u, v, n, self_loops=True), n, n)
+    rowptr, cols = _csr_from_edges(u, v, n, self_loops=True)
     deg = np.diff(rowptr).astype(np.float64)
     dinv = 1.0 / np.sqrt(deg)
     rows = np.repeat(np.arange(n, dtype=np.int64), np.diff(rowptr))
@@ -254,3 +318,35 @@ def make_config(name: str, scale: float = 1.0):
         return gcn_normalized_sbm(n, max(2, int(500 * scale)), 50.0, 0.9,
                                   CONFIG_SEEDS[name]), 256, "float32"
     raise ValueError(name)
+
+
+def cached_config(name: str, scale: float = 1.0, cache_dir=None):
+    """make_config through an on-disk cache: one uncompressed .npz per (configuration, seed,
+    scale) under `cache_dir` (default: $RA_SPMM_GRAPH_CACHE, else <tmp>/ra_spmm_b200_graphs).
+    Ranks of one job call this on rank 0 first and on the others after a barrier, so the
+    10^8-edge graphs are generated once per machine instead of once per process."""
+    import os
+    import tempfile
+    from pathlib import Path
+    root = Path(cache_dir or os.environ.get("RA_SPMM_GRAPH_CACHE")
+                or Path(tempfile.gettempdir()) / "ra_spmm_b200_graphs")
+    path = root / f"{name}_scale{scale:g}_seed{CONFIG_SEEDS[name]}_v1.npz"
+    if path.exists():
+        try:
+            with np.load(path) as z:
+                meta = z["meta"]
+                return (CSR(int(meta[0]), int(meta[1]), z["rowptr"], z["colind"], z["vals"]),
+                        int(meta[2]), "float16" if int(meta[3]) else "float32")
+        except Exception:
+            pass                                   # unreadable file: regenerate
+    a, N, b_dtype = make_config(name, scale)
+    if a.nnz >= (1 << 20):
+        try:
+            root.mkdir(parents=True, exist_ok=True)
+            tmp = path.with_suffix(f".{os.getpid()}.tmp.npz")
+            np.savez(tmp, rowptr=a.rowptr, colind=a.colind, vals=a.vals,
+                     meta=np.array([a.M, a.K, N, 1 if b_dtype == "float16" else 0], dtype=np.int64))
+            os.replace(tmp, path)
+        except OSError:
+            pass                                   # read-only or full disk: run uncached
+    return a, N, b_dtype

@@ -37,6 +37,39 @@ def nnz_balanced_row_splits(rowptr: np.ndarray, parts: int, align: int = 8,
     return bounds
 
 
+def rebalance_by_time(rowptr: np.ndarray, bounds, times_ms, row_weight: float = 1.0,
+                      align: int = 8) -> np.ndarray:
+    """New boundaries from the measured time of every block.
+
+    Block i spans weight w_i (nonzeros + row_weight * rows) and took t_i: inside a block the
+    cost per unit of weight is taken as constant (t_i / w_i), which makes the cumulative cost a
+    piecewise-linear function of the weight coordinate. The new boundaries sit where that
+    function crosses p/P of the total, mapped back to a row and rounded to a multiple of
+    `align` rows. A degree-binned kernel does not cost the same per nonzero in a block of
+    hub rows as in a block of short rows, so a cut by weight alone leaves the blocks unequal;
+    two or three rounds of this update equalise the measured times."""
+    rowptr = np.asarray(rowptr, dtype=np.int64)
+    M = rowptr.size - 1
+    bounds = np.asarray(bounds, dtype=np.int64)
+    parts = bounds.size - 1
+    t = np.maximum(np.asarray(times_ms, dtype=np.float64), 1e-9)
+    assert t.size == parts
+    weight = (rowptr - rowptr[0]).astype(np.float64) + np.arange(M + 1, dtype=np.float64) * row_weight
+    wb = weight[bounds]                                  # weight coordinate of the old boundaries
+    cum_t = np.concatenate([[0.0], np.cumsum(t)])
+    new = bounds.copy()
+    for p in range(1, parts):
+        target = cum_t[-1] * p / parts
+        j = int(min(parts - 1, np.searchsorted(cum_t, target, side="right") - 1))
+        frac = (target - cum_t[j]) / t[j]
+        coord = wb[j] + frac * (wb[j + 1] - wb[j])
+        r = int(np.searchsorted(weight, coord, side="left"))
+        r = min(M, (r + align // 2) // align * align)
+        new[p] = max(new[p - 1], r)
+    new[parts] = M
+    return new
+
+
 L2_BYTES = 126 * 1000 * 1000      # B200 L2 capacity
 
 

@@ -422,14 +422,17 @@ def route(feats: _capi.RaFeatures) -> _capi.RaRoute:
     return out
 
 
-def make_router_plan(rowptr, colind, vals, M, K, N, portfolio="MAIN"):
-    """Decision dict with the keys of plan_to_dict (bindings/ra_bindings.cpp:634-718).
+def route_details(feats: _capi.RaFeatures, r: _capi.RaRoute) -> _capi.RaRouteDetails:
+    out = _capi.RaRouteDetails()
+    _capi.check(_lib().ra_route_details(C.byref(feats), 0, C.byref(r), C.byref(out)), "ra_route_details")
+    return out
 
-    `chosen_path`, `use_tf32`, `decision_reason`, `estimated_risk`,
-    `feasible_by_path` and `feature_values` reproduce the reference for the MAIN
-    portfolio. `scores`, `rejection_codes` and `rejection_details` come from
-    the reference's legacy scoring stage, which the seven-rule block overrides;
-    they are reported as zeros / empty strings here.
+
+def make_router_plan(rowptr, colind, vals, M, K, N, portfolio="MAIN"):
+    """Decision dict with the keys and values of plan_to_dict (bindings/ra_bindings.cpp:634-718)
+    for the MAIN portfolio: the decision (`chosen_path`, `use_tf32`, `decision_reason`,
+    `estimated_risk`, `feasible_by_path`, `feature_values`) and its diagnostics (`scores`,
+    `rejection_codes`, `rejection_details`, gate margins).
     """
     if portfolio != "MAIN":
         raise RaSpmmError("only the MAIN portfolio is implemented (FULL is the "
@@ -437,6 +440,7 @@ def make_router_plan(rowptr, colind, vals, M, K, N, portfolio="MAIN"):
     t0 = time.perf_counter()
     feats = router_features(rowptr, M, K, N)
     r = route(feats)
+    det = route_details(feats, r)
     planning_ms = (time.perf_counter() - t0) * 1e3
     names = _capi.PATH_NAMES
     feas = [bool(r.feasible[i]) for i in range(_capi.PATH_COUNT)]
@@ -453,18 +457,17 @@ def make_router_plan(rowptr, colind, vals, M, K, N, portfolio="MAIN"):
         "decision_reason": r.decision_reason.decode(),
         "estimated_risk": float(r.estimated_risk),
         "planning_time_ms": planning_ms,
-        "gate_margin_raw": 0.0,
-        "gate_margin_norm": 0.0,
+        "gate_margin_raw": float(det.gate_margin_raw),
+        "gate_margin_norm": float(det.gate_margin_norm),
         "path_count": _capi.PATH_COUNT,
         "path_names": list(names),
         "feasible": feas,
         "feasible_by_path": dict(zip(names, feas)),
-        "rejection_codes": {n: ("CHOSEN" if n == chosen else "UNKNOWN") for n in names},
-        "rejection_details": {n: "" for n in names},
+        "rejection_codes": {n: _lib().ra_reject_reason_name(det.rejection_code[i]).decode()
+                            for i, n in enumerate(names)},
+        "rejection_details": {n: det.rejection_detail[i].value.decode() for i, n in enumerate(names)},
         "feature_values": fv,
-        "scores": {k: 0.0 for k in ("csr_direct", "csr_adaptive", "staged_reuse", "tc_sparse",
-                                    "row_split_cuda", "tc_reordered", "hybrid_tc_cuda",
-                                    "cusparse")},
+        "scores": {k: float(det.scores[i]) for i, k in enumerate(_capi.SCORE_KEYS)},
         "feature_set": "production_4",
         "feature_backend": "cuda_rowptr_moments" if rowptr.is_cuda else "cpu_rowptr",
         "total_nnz": int(feats.total_nnz),

@@ -21,7 +21,7 @@ def test_reference_arm_prints_one_contract_line():
     assert line["metric"] == "spmm_gflops_warm" and line["unit"].startswith("GFLOP/s")
     assert line["higher_is_better"] is True and line["n_gpus"] == 1 and line["steps"] == 2
     assert line["value"] > 0 and line["ms_per_step"] > 0
-    assert line["config"]["workload"].startswith("C2")
+    assert line["config"]["workload"].startswith("C4")
     cb = line["cpu_baseline"]
     assert cb["kind"] == "reference" and cb["cores"] >= 1 and cb["value"] == line["value"] and cb["sample"]
     e2e = line["e2e"]

@@ -123,3 +123,26 @@ def test_two_rank_gloo_sharded_spmm():
                        capture_output=True, text=True, env=env, timeout=300)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert "GLOO_OK" in r.stdout
+
+
+def test_rebalance_by_time_equalises_a_two_rate_cost():
+    """Rows of the first half cost 3x per nonzero: a weight cut leaves 3:1 times; the time-driven
+    update converges to equal times, keeps 8-row alignment and monotone boundaries."""
+    rng = np.random.default_rng(0)
+    M = 40000
+    deg = rng.integers(1, 20, size=M)
+    rowptr = np.zeros(M + 1, dtype=np.int64); np.cumsum(deg, out=rowptr[1:])
+    cost_per_row = np.where(np.arange(M) < M // 2, 3.0, 1.0) * deg
+    prefix = np.concatenate([[0.0], np.cumsum(cost_per_row)])
+    block_times = lambda b: [prefix[b[i + 1]] - prefix[b[i]] for i in range(len(b) - 1)]
+    b = P.nnz_balanced_row_splits(rowptr, 4)
+    t0 = block_times(b)
+    assert max(t0) / (sum(t0) / 4) > 1.4
+    for _ in range(3):
+        b = P.rebalance_by_time(rowptr, b, block_times(b))
+        assert b[0] == 0 and b[-1] == M and all(x % 8 == 0 for x in b[:-1]) and all(np.diff(b) >= 0)
+    t = block_times(b)
+    assert max(t) / (sum(t) / 4) < 1.02
+    # equal measured times leave the cut (almost) where it is
+    same = P.rebalance_by_time(rowptr, b, [1.0, 1.0, 1.0, 1.0])
+    assert np.all(np.abs(same - b) <= 8)

@@ -327,3 +327,28 @@ def test_staged_kernels_can_be_switched_off(cuda, kind, N, monkeypatch):
             assert rel_fro(got, want) < 1e-5
     finally:
         monkeypatch.delenv("RA_TC_STAGED", raising=False)
+
+
+def test_a_wait_that_runs_out_is_reported_and_the_plan_stays_usable(cuda, monkeypatch):
+    """Bounded device waits: with a test-only poll limit of zero on the bulk-copy ring every
+    consumer warp gives up on its first stage, records the status word and leaves, and the
+    producer warps still collect, under the normal limit, the copies they had issued. The
+    kernel returns normally, the host reads status 1 (which clears it), and the next run of
+    the same plan is correct."""
+    a = G.chung_lu_power_law(n=16384, seed=5)
+    rp, ci, va = a.torch(cuda)
+    plan = ra_spmm.make_tc_direct_plan(rp, ci, va, a.M, a.K, 64)
+    B = G.dense(a.K, 64, 5).to(cuda)
+    want = ra_spmm.run_tc_direct_plan(plan, B)
+    assert plan.device_status() == 0
+    monkeypatch.setenv("RA_TILE_TMA", "1")
+    monkeypatch.setenv("RA_TILE_TC5", "0")
+    assert rel_fro(ra_spmm.run_tc_direct_plan(plan, B), want.cpu().numpy()) < 1e-6     # the ring itself works
+    assert plan.device_status() == 0
+    monkeypatch.setenv("RA_TILE_TMA_POLL_LIMIT", "0")
+    ra_spmm.run_tc_direct_plan(plan, B)                   # output of this run is not valid
+    assert plan.device_status() == 1                      # kStatusFullTimeout, read and cleared
+    assert plan.device_status() == 0
+    monkeypatch.delenv("RA_TILE_TMA_POLL_LIMIT")
+    assert rel_fro(ra_spmm.run_tc_direct_plan(plan, B), want.cpu().numpy()) < 1e-6
+    assert plan.device_status() == 0

@@ -99,6 +99,16 @@ def test_half_and_tf32_rounding():
     got = np.zeros(x.size, dtype=np.uint16)
     R.oracle_c().oc_f32_to_f16_bits(x.ctypes.data, got.ctypes.data, x.size)
     assert got.tolist() == O.float_to_half_bits(x).tolist()
+    # special values: the bit-twiddling routine of TC_DIRECT sends NaN to the infinity of its sign,
+    # the __float2half_rn of the other two families keeps the canonical NaN
+    neg_nan = np.array([0xFFC00001], dtype=np.uint32).view(np.float32)[0]
+    y = np.array([np.nan, neg_nan, np.inf, -np.inf, 7e4, -7e4, 1e-6, 6e-8, 2.0 ** -24, 0.0, -0.0], dtype=np.float32)
+    got = np.zeros(y.size, dtype=np.uint16)
+    R.oracle_c().oc_f32_to_f16_bits(y.ctypes.data, got.ctypes.data, y.size)
+    assert got.tolist() == O.float_to_half_bits(y, nan_to_inf=True).tolist()
+    assert got[:6].tolist() == [0x7C00, 0xFC00, 0x7C00, 0xFC00, 0x7C00, 0xFC00]
+    other = O.float_to_half_bits(y, nan_to_inf=False)
+    assert other[:2].tolist() == [0x7FFF, 0x7FFF] and other[2:].tolist() == got[2:].tolist()
     t = O.round_tf32(np.array([1.0 + 2.0 ** -11, 1.0 + 2.0 ** -11 + 2.0 ** -20, -(1.0 + 2.0 ** -11)], dtype=np.float32))
     assert t.tolist() == [1.0 + 2.0 ** -10, 1.0 + 2.0 ** -10, -(1.0 + 2.0 ** -10)]   # ties away from zero
 

@@ -122,3 +122,55 @@ def test_config_routes():
     assert O.route_label(O.route(490.0, 0.05, 232960, 256)) == "TC_DIRECT"        # C3
     assert O.route_label(O.route(30.6, 11.3, 4194304, 64)) == "ZERO_OVERHEAD_CSR"  # C4
     assert O.route_label(O.route(51.0, 0.14, 2449029, 47)) == "TC_DIRECT"          # C5
+
+
+def _capi_details(lib, d, cv, M, N):
+    f = _capi.RaFeatures(avg_nnz_per_row=float(d), degree_cv=float(cv), output_dim_N=N, matrix_M=M, matrix_K=M)
+    r = _capi.RaRoute()
+    assert lib.ra_route(C.byref(f), 0, C.byref(r)) == 0
+    det = _capi.RaRouteDetails()
+    assert lib.ra_route_details(C.byref(f), 0, C.byref(r), C.byref(det)) == 0
+    return det
+
+
+def test_scores_and_rejections_against_compiled_reference(lib):
+    """scores (float bits), rejection code and text of every path, and the gate margins: the
+    C ABI and the oracle against the reference's compute_router_scores + route_dispatch."""
+    if R.router() is None or not hasattr(R.router(), "ref_route_details_from_features"):
+        pytest.skip("oracle/_ref/libra_ref_router.so not built with the details export")
+    rng = np.random.default_rng(11)
+    thr_d = [4.5, 5.0, 7.0, 9.0, 12.0, 25.0, 40.0]
+    thr_cv = [0.2, 0.7, 0.8, 1.10, 1.45, 1.5, 1.8, 3.0, 5.0]
+    bits = lambda x: np.float32(x).tobytes()
+    for t in range(3000):
+        d = max(np.float32(rng.choice(thr_d) + rng.choice([0, 1e-6, -1e-6, 0.5, rng.uniform(-5, 600)])), np.float32(0))
+        cv = max(np.float32(rng.choice(thr_cv) + rng.choice([0, 1e-7, -1e-7, 0.05, rng.uniform(-1, 30)])), np.float32(0))
+        M = int(rng.choice([20000, 25000, 149999, 150000, 250000]) + rng.choice([0, -1, 1, rng.integers(0, 2_000_000_000)]))
+        N = int(rng.choice([8, 15, 16, 32, 47, 63, 64, 95, 96, 128, 255, 256, 257, 512, 1024]))
+        ref = R.ref_route_details_from_features(d, 0.0, cv, M, M, N, 0)
+        o = O.route_details(d, cv, M, N)
+        c = _capi_details(lib, d, cv, M, N)
+        for i, k in enumerate(O.SCORE_KEYS):
+            assert bits(ref.scores[i]) == bits(c.scores[i]) == bits(o["scores"][k]), (k, d, cv, M, N)
+        for i, name in enumerate(O.PATH_NAMES):
+            want = (O.REJECT_NAMES[ref.rejection_code[i]], ref.rejection_detail[i].value.decode())
+            assert (lib.ra_reject_reason_name(c.rejection_code[i]).decode(), c.rejection_detail[i].value.decode()) == want, (name, d, cv, M, N)
+            assert (o["rejection_codes"][name], o["rejection_details"][name]) == want, (name, d, cv, M, N)
+        assert bits(ref.gate_margin_raw) == bits(c.gate_margin_raw) == bits(0.0)
+        assert bits(ref.gate_margin_norm) == bits(c.gate_margin_norm) == bits(0.0)
+
+
+def test_scores_and_rejections_against_the_golden_fixture(lib):
+    """Same check against tests/golden/route_details_golden.json (written from the reference's
+    compiled router by make_route_details_golden.py), for boxes without oracle/_ref."""
+    cases = json.loads((Path(__file__).parent / "golden" / "route_details_golden.json").read_text())
+    assert len(cases) >= 20
+    for g in cases:
+        c = _capi_details(lib, g["avg"], g["cv"], g["M"], g["N"])
+        o = O.route_details(g["avg"], g["cv"], g["M"], g["N"])
+        assert [int(np.float32(x).view(np.uint32)) for x in c.scores] == g["score_bits"], g
+        assert [int(np.float32(o["scores"][k]).view(np.uint32)) for k in O.SCORE_KEYS] == g["score_bits"], g
+        assert [lib.ra_reject_reason_name(x).decode() for x in c.rejection_code] == g["codes"], g
+        assert [c.rejection_detail[i].value.decode() for i in range(len(O.PATH_NAMES))] == g["details"], g
+        assert [o["rejection_codes"][n] for n in O.PATH_NAMES] == g["codes"]
+        assert [o["rejection_details"][n] for n in O.PATH_NAMES] == g["details"]
