@@ -74,6 +74,8 @@ def parse_args():
                          "(default: 3 for the CSR kernels, 1 for the tile kernels); the cut is then tuned from measured times")
     ap.add_argument("--balance-rounds", type=int, default=3,
                     help="multi-GPU: rounds of measuring every rank's block and moving the boundaries")
+    ap.add_argument("--gcn-panels", type=int, default=1,
+                    help="multi-GPU GCN step: column panels per all-gather (SpMM of a panel overlaps the next gather)")
     ap.add_argument("--emulate-ranks", type=int, default=0,
                     help="diagnostic, one GPU: cut the rows as for this many ranks, time the blocks one after the other "
                          "and report the balance (no JSON contract line)")
@@ -406,7 +408,7 @@ def traffic_entry(cfg, kernel):
         return None, None
     if isinstance(e, dict):
         return e.get("bytes"), e.get("source")
-    return e, "profiles/dram_traffic.json"
+    return (e, "profiles/dram_traffic.json") if e is not None else (None, None)
 
 
 def measure_entry(torch, dist, args, cfg, selector, dev, world, rank, peak):
@@ -679,6 +681,23 @@ def main():
                 also.append(measure_entry(torch, dist, args, cfg, sel, dev, world, rank, peak))
             except Exception as exc:                # one entry failing must not lose the headline
                 also.append({"config": cfg, "selector": sel, "error": f"{type(exc).__name__}: {exc}"})
+        # configuration 5: the 2-layer GCN training step on the row-partitioned operator
+        # (forward + backward + Adam; NCCL all-gather of each layer's row slabs at N > 1)
+        try:
+            from ra_spmm_b200 import gcn_bench
+            gargs = gcn_bench.parse_args(["--scale", str(args.scale), "--steps", "10", "--warmup", "3",
+                                          "--panels", str(args.gcn_panels if dist_on else 1)])
+            g = gcn_bench.measure(gargs, world, rank, dev)
+            if rank == 0:
+                also.append({"config": "C5", "kernel": "2-layer GCN step, routed SpMM (" +
+                             ", ".join(f"N={k}: {v}" for k, v in sorted(g["config"]["labels"].items())) + ")",
+                             "gcn_step_ms": g["value"], "spmm_gflops": g["spmm_gflops"], "loss": g["loss"],
+                             "steps": g["steps"], "warmup": g["warmup"], "workload": g["config"]["workload"],
+                             "allgather_bytes_per_step_per_rank": g["config"]["allgather_bytes_per_step_per_rank"],
+                             "panels": g["config"]["panels"]})
+        except Exception as exc:
+            if rank == 0:
+                also.append({"config": "C5", "error": f"{type(exc).__name__}: {exc}"})
         if rank == 0:
             line["also"] = also
             line["gpu_launches"] += sum(e.get("iters", 0) for e in also) * n_gpus

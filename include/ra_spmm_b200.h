@@ -263,6 +263,18 @@ RA_API int ra_tile_plan_destroy(RaTilePlan* plan);
  * non-zero status clears it. The reference kernels have no waits and no counterpart. */
 RA_API int ra_tile_plan_device_status(RaTilePlan* plan, int* status);
 
+/* ---- plan files ----------------------------------------------------------
+ * A built plan written to a file and read back in another process. The reference keeps its
+ * plans (ra_common.h:507-530, 593-719) in memory only and rebuilds them per process; its
+ * experiments/verify_format_checksums.py compares per-array checksums of the formats across
+ * runs. The file stores every plan array with its length and 64-bit FNV-1a checksum; *_load
+ * recomputes the checksums while uploading and fails (RA_ERR_INVALID_ARG, nothing returned)
+ * on a truncated or altered file. Lazily grown scratch is not part of the file. */
+RA_API int ra_zo_plan_save(const RaZoPlan* plan, const char* path);
+RA_API int ra_zo_plan_load(const char* path, RaZoPlan** out);
+RA_API int ra_tile_plan_save(const RaTilePlan* plan, const char* path);
+RA_API int ra_tile_plan_load(const char* path, RaTilePlan** out);
+
 #ifdef __cplusplus
 }
 #endif

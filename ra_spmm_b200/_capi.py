@@ -32,6 +32,7 @@ EXPORTED_SYMBOLS = [
     "ra_zo_plan_create", "ra_zo_plan_info", "ra_zo_plan_run", "ra_zo_plan_destroy",
     "ra_zo_plan_run_phases", "ra_zo_plan_run_noalloc",
     "ra_tile_plan_create", "ra_tile_plan_info", "ra_tile_plan_run", "ra_tile_plan_destroy", "ra_tile_plan_device_status",
+    "ra_zo_plan_save", "ra_zo_plan_load", "ra_tile_plan_save", "ra_tile_plan_load",
 ]
 
 
@@ -137,6 +138,10 @@ def load() -> C.CDLL:
     lib.ra_tile_plan_run.argtypes = [vp, i32, vp, i32, vp, i32, vp]
     lib.ra_tile_plan_destroy.argtypes = [vp]
     lib.ra_tile_plan_device_status.argtypes = [vp, C.POINTER(C.c_int)]
+    lib.ra_zo_plan_save.argtypes = [vp, C.c_char_p]
+    lib.ra_zo_plan_load.argtypes = [C.c_char_p, C.POINTER(vp)]
+    lib.ra_tile_plan_save.argtypes = [vp, C.c_char_p]
+    lib.ra_tile_plan_load.argtypes = [C.c_char_p, C.POINTER(vp)]
     for name in EXPORTED_SYMBOLS:
         fn = getattr(lib, name)
         if fn.restype is C.c_int and name not in ("ra_version",):

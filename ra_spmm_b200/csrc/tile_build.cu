@@ -102,12 +102,16 @@ tb_window_bounds_kernel(const unsigned long long* __restrict__ keys, i64 n, int 
 
 __global__ void __launch_bounds__(kTbThreads)
 tb_window_blocks_kernel(const int* __restrict__ ws, const int* __restrict__ hscan, int W,
-                        int* __restrict__ blocks)
+                        int* __restrict__ blocks, int* __restrict__ max_blocks)
 {
+    int local_max = 0;
     for (i64 w = (i64)blockIdx.x * blockDim.x + threadIdx.x; w < W; w += (i64)gridDim.x * blockDim.x) {
         const int nvec = hscan[ws[w + 1]] - hscan[ws[w]];
-        blocks[w] = (nvec + kVecPerBlock - 1) / kVecPerBlock;
+        const int nb = (nvec + kVecPerBlock - 1) / kVecPerBlock;
+        blocks[w] = nb;
+        local_max = max(local_max, nb);
     }
+    if (local_max > 0) atomicMax(max_blocks, local_max);
 }
 
 // fp32 -> fp16 bits, round to nearest even. The reference converts on the host with two
@@ -355,13 +359,16 @@ extern "C" int ra_tile_plan_create(int kind, const int32_t* rowptr, const int32_
     TB_TRY(exclusive_scan_i32(hs.as<int>(), hs.as<int>(), n, tmp.as<int>(), st));
     tb_window_bounds_kernel<<<grid_for((i64)W + 1), kTbThreads, 0, st>>>(skeys, n, W, shift_w, wsb.as<int>());
     TB_TRY(cudaGetLastError());
-    tb_window_blocks_kernel<<<grid_for(W), kTbThreads, 0, st>>>(wsb.as<int>(), hs.as<int>(), W, blk.as<int>());
+    TB_TRY(cudaMalloc(reinterpret_cast<void**>(&p->d_status), sizeof(int)));     // doubles as the max-reduction cell here
+    TB_TRY(cudaMemsetAsync(p->d_status, 0, sizeof(int), st));
+    tb_window_blocks_kernel<<<grid_for(W), kTbThreads, 0, st>>>(wsb.as<int>(), hs.as<int>(), W, blk.as<int>(), p->d_status);
     TB_TRY(cudaGetLastError());
     TB_TRY(cudaMalloc(reinterpret_cast<void**>(&p->d_block_offsets), sizeof(int) * ((size_t)W + 1)));
     TB_TRY(exclusive_scan_i32(blk.as<int>(), p->d_block_offsets, W, tmp.as<int>(), st));
     int total_blocks = 0, total_vectors = 0;
     TB_TRY(cudaMemcpyAsync(&total_blocks, p->d_block_offsets + W, sizeof(int), cudaMemcpyDeviceToHost, st));
     TB_TRY(cudaMemcpyAsync(&total_vectors, hs.as<int>() + n, sizeof(int), cudaMemcpyDeviceToHost, st));
+    TB_TRY(cudaMemcpyAsync(&p->max_window_blocks, p->d_status, sizeof(int), cudaMemcpyDeviceToHost, st));
     TB_TRY(cudaStreamSynchronize(st));
 
     // ---- fill atox / vals_f16 ------------------------------------------------
@@ -435,8 +442,7 @@ extern "C" int ra_tile_plan_create(int kind, const int32_t* rowptr, const int32_
         TB_TRY(cudaGetLastError());
         TB_TRY(cudaStreamSynchronize(st));
     }
-    TB_TRY(cudaMalloc(reinterpret_cast<void**>(&p->d_status), sizeof(int)));
-    TB_TRY(cudaMemsetAsync(p->d_status, 0, sizeof(int), st));
+    TB_TRY(cudaMemsetAsync(p->d_status, 0, sizeof(int), st));         // allocated above (held the window maximum)
     TB_TRY(cudaStreamSynchronize(st));   // temporaries are freed on return
 #undef TB_TRY
     p->active = 1;

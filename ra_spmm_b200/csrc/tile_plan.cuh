@@ -20,6 +20,7 @@ struct RaTilePlan {
     int M = 0, K = 0;
     int num_windows = 0;
     long long num_blocks = 0;
+    int max_window_blocks = 0;        // blocks of the largest window (engine choice at run time)
     long long nnz = 0;
     float tile_density = 0.f;
     int* d_block_offsets = nullptr;

@@ -27,7 +27,7 @@
 //     (fp16) or conflict-free 32-bit loads (tf32). The ring runs ahead across
 //     unit boundaries, so short windows do not drain the pipeline.
 //   * gather indices (atox) are prefetched four blocks per coalesced load.
-#include "tile_plan.cuh"
+#include "tile_common.cuh"
 
 #include <algorithm>
 #include <cstdlib>
@@ -44,86 +44,6 @@ constexpr int kRowBytesF16 = 128 + 16;   // 64 halves + pad: ldmatrix rows hit d
 constexpr int kRowBytesF32 = 128 + 32;   // 32 floats + pad: (8k + g) mod 32 distinct
 constexpr int kStageF16    = 8 * kRowBytesF16 + 128;   // + packed sparse block
 constexpr int kStageF32    = 8 * kRowBytesF32 + 128;
-
-struct TileArgs {
-    const int* block_offsets;
-    const int* atox;
-    const uint16_t* vals;
-    const unsigned long long* val_masks;   // zero-compressed plans (vals is null)
-    const int* val_base;
-    const uint16_t* vals_zc;
-    const int* win_rows;
-    const int* seg_window;
-    const int* seg_bbegin;
-    const int* seg_bend;
-    const int* seg_scratch;
-    int num_units;
-    int M;
-    int N;
-    int ldb;                   // row stride of the B operand in elements (N, or N rounded up to 16
-                               // when the library made a padded fp16 copy)
-    long long total_blocks;
-    float* C;
-    float* scratch;
-};
-
-__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gsrc) {
-    const unsigned s = (unsigned)__cvta_generic_to_shared(smem_dst);
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(s), "l"(gsrc) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int kPending>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" :: "n"(kPending) : "memory"); }
-
-__device__ __forceinline__ void mma_f16_m16n8k8(float (&d)[4], unsigned a0, unsigned a1, unsigned b0) {
-    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
-                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(b0));
-}
-__device__ __forceinline__ void mma_tf32_m16n8k8(float (&d)[4], unsigned a0, unsigned a1, unsigned a2,
-                                                 unsigned a3, unsigned b0, unsigned b1) {
-    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ unsigned to_tf32_rna(float x) {
-    unsigned r = __float_as_uint(x);
-    asm("cvt.rna.tf32.f32 %0, %0;" : "+r"(r));
-    return r;
-}
-
-// Zero-compressed value of (vector k, window row r) of a block: bit k*8+r of the mask says
-// whether it is stored; stored values are packed in bit order from `base` on
-// (same format as zc_val_bits, tc/ra_tc_direct.cu:402-414).
-__device__ __forceinline__ unsigned zc_value_bits(unsigned long long mask, int base,
-                                                  const uint16_t* __restrict__ vals_zc, int k, int r) {
-    const int bit = k * 8 + r;
-    if (!((mask >> bit) & 1ull)) return 0u;
-    const unsigned long long below = mask & ((1ull << bit) - 1ull);
-    return (unsigned)__ldg(vals_zc + base + __popcll(below));
-}
-
-// first block of unit u (u == num_units gives the total)
-template <int kMode>
-__device__ __forceinline__ long long unit_begin(const TileArgs& a, int u) {
-    if (u >= a.num_units) return a.total_blocks;
-    return (kMode == 2) ? (long long)__ldg(a.seg_bbegin + u) : (long long)__ldg(a.block_offsets + u);
-}
-template <int kMode>
-__device__ __forceinline__ int unit_lower_bound(const TileArgs& a, long long target) {
-    int lo = 0, hi = a.num_units;          // smallest u with unit_begin(u) + u >= target
-    while (lo < hi) {
-        const int mid = (lo + hi) >> 1;
-        if (unit_begin<kMode>(a, mid) + mid < target) lo = mid + 1; else hi = mid;
-    }
-    return lo;
-}
-
-__device__ __forceinline__ void mma_f16_m16n8k16(float (&d)[4], unsigned a0, unsigned a1, unsigned a2,
-                                                 unsigned a3, unsigned b0, unsigned b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
 
 // kMode: 0 natural windows, 1 window-row table (COMMUNITY_TC), 2 segments.
 // kMT: 16-feature tiles per warp slice (4 for fp16, 2 for tf32).
@@ -395,42 +315,6 @@ tile_spmm_kernel(TileArgs a, const void* __restrict__ Bmat, int slices, int grou
 // still multiplies its own 128-byte column slice. Every wait is bounded: after
 // kSpinLimit polls the warp records an error code in the status word and returns.
 // ---------------------------------------------------------------------------
-constexpr int kSpinLimit = 1 << 22;
-enum { kStatusFullTimeout = 1, kStatusEmptyTimeout = 2 };
-
-__device__ __forceinline__ void mbar_init(unsigned addr, int count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(addr), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(unsigned addr, unsigned bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(addr), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(unsigned addr) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(addr) : "memory");
-}
-__device__ __forceinline__ bool mbar_wait(unsigned addr, unsigned parity, int limit = kSpinLimit) {
-    for (int i = 0; i < limit; ++i) {
-        unsigned ok;
-        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                     : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
-        if (ok) return true;
-    }
-    return false;
-}
-// Whole-warp form: the 32 lanes poll together and agree on the outcome, so the code after the
-// wait (warp-synchronous shared-memory reads) never runs with a part of the warp.
-__device__ __forceinline__ bool mbar_wait_warp(unsigned addr, unsigned parity, int limit) {
-    for (int i = 0; i < limit; ++i) {
-        unsigned ok;
-        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                     : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
-        if (__all_sync(0xffffffffu, ok != 0u)) return true;
-    }
-    return false;
-}
-__device__ __forceinline__ void bulk_copy_g2s(unsigned dst, const void* src, unsigned bytes, unsigned mbar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 :: "r"(dst), "l"(src), "r"(bytes), "r"(mbar) : "memory");
-}
 
 template <bool kTF32, int kMode>
 __global__ void __launch_bounds__(256)
@@ -1077,14 +961,25 @@ static int launch_tile(const TileArgs& a, const void* B, bool staged, cudaStream
         groups = std::min(groups, std::max<long long>(1, weight / 48));
         const int ctas = (int)((groups + groups_per_cta - 1) / groups_per_cta);
         groups = (long long)ctas * groups_per_cta;
-        // tcgen05 / TMEM path (FP16 only). Measured on B200 against the mma.sync ring: 1.2-1.5x
-        // faster at N = 128 (one full 128-feature panel per MMA), on par at N = 256 (both bound by
-        // the L2 gather), slower at N = 64 (half of every panel is padding). Default: N in (96, 128];
-        // RA_TILE_TC5=1 / 0 forces it on (N <= 512) / off.
+        // Engine choice. tcgen05 / TMEM path (FP16 only): measured on B200 1.2-1.5x faster than the
+        // per-warp rings at N = 128 (one full 128-feature panel per MMA), no better at other widths.
+        // TMA gather ring (tile_gather4.cu): faster than the cp.async ring on every other shape it
+        // covers (C3 FP16 N=256 4.9 vs 6.4 ms, C4 TF32 N=64 4.4 vs 5.0 ms). RA_TILE_TC5=1/0 and
+        // RA_TILE_G4=1/0 force an engine on or off.
         const char* tc5_env = std::getenv("RA_TILE_TC5");
         const bool tc5_auto = a.N > 96 && a.N <= 128;
-        const bool use_tc5 = tc5_env ? (tc5_env[0] == '1') : tc5_auto;
-        if (!kZC && !padded && !kTF32 && use_tc5 && a.N <= 512) {
+        const bool use_tc5 = !kZC && !padded && !kTF32 && a.N <= 512 && (tc5_env ? (tc5_env[0] == '1') : tc5_auto);
+        const char* g4_env = std::getenv("RA_TILE_G4");
+        // a warp of the TMA ring has at most three blocks in flight, so it walks one unit slower than
+        // a warp of the 8-stage cp.async ring: units of thousands of blocks (hub windows of TC_DIRECT /
+        // COMMUNITY_TC on power-law graphs) stay on the cp.async ring
+        const bool g4_auto = !use_tc5 && a.max_unit_blocks <= 1024;
+        const bool use_g4 = !kZC && (g4_env ? (g4_env[0] == '1') : g4_auto);
+        if (use_g4) {
+            const int rc = launch_tile_gather4<kTF32, kMode>(a, B, a.K, st, status);
+            if (rc != RA_ERR_UNSUPPORTED) return rc;
+        }
+        if (use_tc5) {
             const int panels = (a.N + 127) / 128;
             const size_t smem5 = (size_t)kTcStages * (panels * 4096 + 1024) + 1024;
             const int per_sm = (int)std::max<size_t>(1, std::min<size_t>(8, (200 * 1024) / (smem5 + 1024)));
@@ -1213,7 +1108,8 @@ extern "C" int ra_tile_plan_run(RaTilePlan* p, int precision, const void* d_B, i
     a.seg_window = p->d_seg_window; a.seg_bbegin = p->d_seg_bbegin; a.seg_bend = p->d_seg_bend;
     a.seg_scratch = p->d_seg_scratch;
     a.num_units = (p->kind == RA_TILE_SEGMENT_HYBRID) ? p->num_segments : p->num_windows;
-    a.M = p->M; a.N = N; a.ldb = ldb; a.total_blocks = p->num_blocks;
+    a.M = p->M; a.K = p->K; a.N = N; a.ldb = ldb; a.total_blocks = p->num_blocks;
+    a.max_unit_blocks = (p->kind == RA_TILE_SEGMENT_HYBRID) ? std::min(p->max_window_blocks, kSegBlocks) : p->max_window_blocks;
     a.C = d_C; a.scratch = p->d_scratch;
 
     // RA_TC_STAGED=0 keeps the direct-load kernels, as in the reference (tc/ra_tc_direct.cu:837-838)

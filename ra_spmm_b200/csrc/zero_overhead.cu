@@ -21,8 +21,10 @@
 // The reference adds multi-chunk partials with fp32 atomicAdd in arbitrary
 // order; here the merge order is fixed, so results are run-to-run identical.
 #include "csr_engine.cuh"
+#include "csr_chunk.cuh"
 #include "csr_stream.cuh"
 #include "scan.cuh"
+#include "zo_plan.cuh"
 
 #include <cstdlib>
 #include <mutex>
@@ -207,20 +209,6 @@ zo_finish_kernel(const int* __restrict__ zero_ids, const int* __restrict__ zero_
 }  // namespace ra
 
 // ---- C ABI ----------------------------------------------------------------------
-struct RaZoPlan {
-    int M = 0, K = 0;
-    int num_tiny = 0, num_short = 0, num_medium = 0, num_long = 0, num_empty = 0;
-    int num_small = 0, num_chunks = 0, num_zero_rows = 0, max_long_chunks = 0;
-    int num_slots = 0;
-    int* d_small_row_ids = nullptr;
-    int* d_chunk_rows = nullptr;
-    int* d_chunk_starts = nullptr;
-    int* d_chunk_slot = nullptr;      // derived: scratch slot per chunk, -1 = sole
-    int* d_zero_row_ids = nullptr;
-    int* d_zero_slot_off = nullptr;   // derived: [num_zero_rows+1] slot ranges
-    float* d_scratch = nullptr;       // lazily grown: num_slots * N floats
-    size_t scratch_bytes = 0;
-};
 
 extern "C" int ra_zo_plan_destroy(RaZoPlan* p)
 {
@@ -378,15 +366,30 @@ int zo_run_with_scratch(const RaZoPlan* p, float* scratch, const int* d_rowptr,
     RaZoPlan view = *p;            // shallow copy that carries the scratch pointer
     view.d_scratch = scratch;
     // RA_ZO_CHUNK_ENGINE=register runs the chunks on the register engine (diagnostic switch)
-    static const bool chunk_register = [] {
-        const char* e = std::getenv("RA_ZO_CHUNK_ENGINE");
-        return e && std::string(e) == "register";
-    }();
+    const char* engine_env = std::getenv("RA_ZO_CHUNK_ENGINE");
+    const std::string engine = engine_env ? engine_env : "";
+    const bool chunk_register = engine == "register";
+    // RA_ZO_CHUNK_ENGINE=lean: the chunks run on the short-path chunk kernel (csr_chunk.cuh) and the
+    // small rows follow in their own launch
+    const bool chunk_lean = engine == "lean" && wide_ok && stream_aligned_width_ok(N);
+    const bool chunk_reg2 = engine == "reg2" && wide_ok && stream_aligned_width_ok(N);
     // A matrix made of long rows (nearly all work in chunks) at N >= 256 runs faster on the
     // register engine, as CSR_DIRECT does there: full chunks keep enough loads in flight and
     // every gathered byte crosses the shared-memory data path once.
     const bool long_rows = N >= 256 && (long long)p->num_chunks >= 16ll * p->num_small;
     const bool chunk_stream = wide_ok && stream_aligned_width_ok(N) && !chunk_register && !long_rows;
+    if (p->num_chunks > 0 && (phase_mask & 1) && chunk_reg2) {
+        const int rc = launch_zo_chunks_reg(d_rowptr, d_colind, d_vals, d_B, d_C, scratch, p->d_chunk_rows,
+                                            p->d_chunk_starts, p->d_chunk_slot, p->num_chunks, N, st);
+        if (rc != RA_OK) return rc;
+        phase_mask &= ~1;
+    }
+    if (p->num_chunks > 0 && (phase_mask & 1) && chunk_lean) {
+        const int rc = launch_zo_chunks_lean(d_rowptr, d_colind, d_vals, d_B, d_C, scratch, p->d_chunk_rows,
+                                             p->d_chunk_starts, p->d_chunk_slot, p->num_chunks, N, st);
+        if (rc != RA_OK) return rc;
+        phase_mask &= ~1;
+    }
     if (p->num_chunks > 0 && p->num_small > 0 && (phase_mask & 3) == 3 && chunk_stream) {
         // chunks and small rows in one launch: the chunk warps (the long items) start first
         StreamArgs a{};

@@ -1,9 +1,10 @@
-"""2-layer GCN training step on top of the SpMM kernels, single- or multi-GPU.
+"""2-layer GNN training steps (GCN, GraphSAGE-mean, GIN) on top of the SpMM kernels,
+single- or multi-GPU.
 
-Mirrors the reference harness for the GCN configuration
-(gnn_bench/router_vs_baselines_gcn.py: GraphBackend :140-410, SparseMMFunction
-:448-461, GCNBench :464-476, measure_step :482-498): bias-free Linear layers,
-h = relu(A (X W1)), out = A (h W2), cross-entropy, Adam.
+Mirrors the reference harnesses (gnn_bench/router_vs_baselines_gcn.py: aggregation operators
+:89-126, GraphBackend :140-410, SparseMMFunction :448-461, GCNBench :464-476, measure_step
+:482-498; router_vs_baselines_sage.py:48-67; router_vs_baselines_gin.py:47-74): bias-free
+Linear layers, cross-entropy, Adam; GCN h = relu(A (X W1)), out = A (h W2).
 
 Multi-GPU (not in the reference): A is row-partitioned, every rank owns the rows
 [b[r], b[r+1]) of X, H, the logits and the labels. Each SpMM needs all rows of its
@@ -13,7 +14,10 @@ indices address directly; when the kernel reads fp16, the slab is rounded to fp1
 before the gather, not after); the backward of
 an SpMM is the same operation with the transposed operator: grad_in_local =
 (A^T)[rows] @ allgather(grad_out). For the symmetric GCN operator A^T = A, so
-one plan serves both directions. Weight gradients are all-reduced.
+one plan serves both directions; the row-mean operator of GraphSAGE is not symmetric and
+gets a second operator built from the transposed row block (`transpose_csr`). Weight
+gradients are all-reduced. With `panels` > 1 a wide operand is gathered in column panels and
+the SpMM of panel j runs while panel j+1 is still on NVLink.
 """
 from __future__ import annotations
 
@@ -24,6 +28,51 @@ import torch
 import torch.distributed as dist
 import torch.nn as nn
 import torch.nn.functional as F
+
+
+def aggregation_operator(rowptr, colind, M: int, model: str, vals=None):
+    """Per-model aggregation matrix from a raw adjacency (CSR, duplicate-free), as
+    build_aggregation_operator does (gnn_bench/router_vs_baselines_gcn.py:89-126):
+      gcn  : D~^-1/2 (A + I) D~^-1/2, the diagonal added only where absent;
+      sage : D^-1 A (row mean; zero-degree rows stay zero, no self loop);
+      gin  : A unchanged.
+    Arithmetic in float64, result (rowptr int32, colind int32, vals float32) with sorted columns."""
+    rowptr = np.asarray(rowptr, dtype=np.int64)
+    colind = np.asarray(colind, dtype=np.int64)
+    w = np.ones(colind.size, dtype=np.float64) if vals is None else np.asarray(vals, dtype=np.float64)
+    rows = np.repeat(np.arange(M, dtype=np.int64), np.diff(rowptr))
+    m = model.lower()
+    if m == "gcn":
+        has_diag = np.zeros(M, dtype=bool)
+        has_diag[rows[rows == colind]] = True
+        add = np.flatnonzero(~has_diag)
+        rows = np.concatenate([rows, add]); colind = np.concatenate([colind, add])
+        w = np.concatenate([w, np.ones(add.size)])
+    order = np.lexsort((colind, rows))
+    rows, colind, w = rows[order], colind[order], w[order]
+    if m == "gcn":
+        d = np.bincount(rows, weights=w, minlength=M)
+        dis = np.divide(1.0, np.sqrt(d), out=np.zeros_like(d), where=d > 0)
+        w = dis[rows] * w * dis[colind]
+    elif m in ("sage", "graphsage"):
+        d = np.bincount(rows, weights=w, minlength=M)
+        w = w * np.divide(1.0, d, out=np.zeros_like(d), where=d > 0)[rows]
+    elif m != "gin":
+        raise ValueError(f"unknown model for aggregation operator: {model}")
+    rp = np.zeros(M + 1, dtype=np.int64)
+    np.cumsum(np.bincount(rows, minlength=M), out=rp[1:])
+    return rp.astype(np.int32), colind.astype(np.int32), w.astype(np.float32)
+
+
+def transpose_csr(rowptr, colind, vals, M: int, K: int):
+    """CSR of A^T (K x M), columns sorted: the operator of the backward pass when A is not
+    symmetric (GraphBackend builds it with scipy, gnn_bench/router_vs_baselines_gcn.py:166-168)."""
+    rowptr = np.asarray(rowptr, dtype=np.int64)
+    rows = np.repeat(np.arange(M, dtype=np.int64), np.diff(rowptr))
+    order = np.argsort(np.asarray(colind), kind="stable")          # by column, rows stay ascending
+    rp = np.zeros(K + 1, dtype=np.int64)
+    np.cumsum(np.bincount(np.asarray(colind), minlength=K), out=rp[1:])
+    return rp.astype(np.int32), rows[order].astype(np.int32), np.asarray(vals)[order]
 
 
 class GraphOperator:
@@ -94,6 +143,11 @@ class GraphOperator:
                 else m.run_segment_hybrid_plan(plan, self.ci, self.va, B))
 
 
+class _Done:
+    def wait(self):
+        return True
+
+
 class RowSharding:
     """Row boundaries of the partition and the collective that rebuilds a full
     dense operand from the ranks' row slabs.
@@ -127,9 +181,10 @@ class RowSharding:
         owner = np.searchsorted(b, colind, side="right") - 1
         return (owner * self.max_rows + (colind - b[owner])).astype(np.int32)
 
-    def all_gather_rows(self, local: torch.Tensor) -> torch.Tensor:
+    def all_gather_rows(self, local: torch.Tensor, async_op: bool = False):
+        """Gathered operand; with async_op the pair (operand, work handle to wait on)."""
         if self.world == 1:
-            return local
+            return (local, _Done()) if async_op else local
         n = local.shape[1]
         full = torch.empty((self.world * self.max_rows, n), dtype=local.dtype, device=local.device)
         r0, r1 = self.rows
@@ -138,14 +193,35 @@ class RowSharding:
         else:                                   # pad this rank's slab to the common height
             src = torch.zeros((self.max_rows, n), dtype=local.dtype, device=local.device)
             src[: r1 - r0].copy_(local)
-        dist.all_gather_into_tensor(full, src, group=self.group)
+        work = dist.all_gather_into_tensor(full, src, group=self.group, async_op=async_op)
         self.comm_bytes += full.numel() * full.element_size()
-        return full
+        return (full, work) if async_op else full
 
 
-def _gather_and_multiply(local, spmm: Callable, sharding: RowSharding, fmt):
-    """all-gather the row slabs (in the operand format of the kernel when `fmt` is given), SpMM."""
+def _gather_and_multiply(local, spmm: Callable, sharding: RowSharding, fmt, panels: int = 1):
+    """all-gather the row slabs (in the operand format of the kernel when `fmt` is given), SpMM.
+    panels > 1: the operand is cut into that many column panels (each at least 32 columns and a
+    multiple of 16); all panel gathers are queued at once and the SpMM of a panel starts as soon
+    as its own gather has landed, so it overlaps the gathers behind it."""
     n = local.shape[1]
+    if sharding.world > 1 and panels > 1 and n % (16 * panels) == 0 and n // panels >= 32:
+        w = n // panels
+        pending = []
+        for j in range(panels):
+            src = local[:, j * w:(j + 1) * w]
+            if fmt is not None:
+                dtype, width = fmt(w)
+                assert width == w
+                src = src.to(dtype)
+            pending.append(sharding.all_gather_rows(src.contiguous(), async_op=True))
+        out = None
+        for j, (full, work) in enumerate(pending):
+            work.wait()
+            part = spmm(full)
+            if out is None:
+                out = part.new_empty((part.shape[0], n))
+            out[:, j * w:(j + 1) * w] = part
+        return out
     if sharding.world > 1 and fmt is not None:
         dtype, width = fmt(n)
         if dtype != local.dtype or width != n:
@@ -161,19 +237,19 @@ def _gather_and_multiply(local, spmm: Callable, sharding: RowSharding, fmt):
 
 class _ShardedSpMM(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, H_local, spmm: Callable, spmm_t: Callable, sharding: RowSharding, fmt, fmt_t):
-        ctx.spmm_t, ctx.sharding, ctx.fmt_t = spmm_t, sharding, fmt_t
-        return _gather_and_multiply(H_local.detach(), spmm, sharding, fmt)
+    def forward(ctx, H_local, spmm: Callable, spmm_t: Callable, sharding: RowSharding, fmt, fmt_t, panels):
+        ctx.spmm_t, ctx.sharding, ctx.fmt_t, ctx.panels = spmm_t, sharding, fmt_t, panels
+        return _gather_and_multiply(H_local.detach(), spmm, sharding, fmt, panels)
 
     @staticmethod
     def backward(ctx, grad_out):
-        g = _gather_and_multiply(grad_out.contiguous(), ctx.spmm_t, ctx.sharding, ctx.fmt_t)
-        return g, None, None, None, None, None
+        g = _gather_and_multiply(grad_out.contiguous(), ctx.spmm_t, ctx.sharding, ctx.fmt_t, ctx.panels)
+        return g, None, None, None, None, None, None
 
 
-def sharded_spmm(H_local, spmm, spmm_t, sharding, operand_format=None, operand_format_t=None):
+def sharded_spmm(H_local, spmm, spmm_t, sharding, operand_format=None, operand_format_t=None, panels=1):
     return _ShardedSpMM.apply(H_local, spmm, spmm_t, sharding, operand_format,
-                              operand_format_t or operand_format)
+                              operand_format_t or operand_format, panels)
 
 
 class GCN2(nn.Module):
@@ -182,21 +258,67 @@ class GCN2(nn.Module):
 
     def __init__(self, in_dim: int, hidden: int, out_dim: int, spmm: Callable,
                  spmm_t: Optional[Callable] = None, sharding: Optional[RowSharding] = None,
-                 operand_format: Optional[Callable] = None):
+                 operand_format: Optional[Callable] = None, operand_format_t: Optional[Callable] = None,
+                 panels: int = 1):
         super().__init__()
         self.lin1 = nn.Linear(in_dim, hidden, bias=False)
         self.lin2 = nn.Linear(hidden, out_dim, bias=False)
-        self.spmm, self.spmm_t = spmm, spmm_t or spmm
-        self.sharding = sharding or RowSharding([0, 0])
-        self.operand_format = operand_format      # GraphOperator.operand_format, or None = gather as is
+        _attach(self, spmm, spmm_t, sharding, operand_format, operand_format_t, panels)
 
     def forward(self, X_local):
-        h = sharded_spmm(self.lin1(X_local), self.spmm, self.spmm_t, self.sharding, self.operand_format)
-        h = F.relu(h)
-        return sharded_spmm(self.lin2(h), self.spmm, self.spmm_t, self.sharding, self.operand_format)
+        h = F.relu(self.aggregate(self.lin1(X_local)))
+        return self.aggregate(self.lin2(h))
 
 
-def train_step(model: GCN2, opt, X_local, y_local, total_rows: int):
+def _attach(module, spmm, spmm_t, sharding, operand_format, operand_format_t, panels):
+    module.spmm, module.spmm_t = spmm, spmm_t or spmm
+    module.sharding = sharding or RowSharding([0, 0])
+    module.operand_format = operand_format        # GraphOperator.operand_format, or None = gather as is
+    module.operand_format_t = operand_format_t or operand_format
+    module.panels = panels
+    module.aggregate = lambda H: sharded_spmm(H, module.spmm, module.spmm_t, module.sharding,
+                                              module.operand_format, module.operand_format_t, module.panels)
+
+
+class SAGE2(nn.Module):
+    """GraphSAGE with the mean aggregator: h = relu(W1 [x | A x]), out = W2 [h | A h], A = D^-1 Adj
+    (SAGEBench, gnn_bench/router_vs_baselines_sage.py:48-67). A is not symmetric: pass the operator
+    of the transposed row block as `spmm_t`."""
+
+    def __init__(self, in_dim: int, hidden: int, out_dim: int, spmm: Callable, spmm_t: Callable,
+                 sharding: Optional[RowSharding] = None, operand_format: Optional[Callable] = None,
+                 operand_format_t: Optional[Callable] = None, panels: int = 1):
+        super().__init__()
+        self.lin1 = nn.Linear(2 * in_dim, hidden, bias=False)
+        self.lin2 = nn.Linear(2 * hidden, out_dim, bias=False)
+        _attach(self, spmm, spmm_t, sharding, operand_format, operand_format_t, panels)
+
+    def forward(self, X_local):
+        h = F.relu(self.lin1(torch.cat([X_local, self.aggregate(X_local)], dim=1)))
+        return self.lin2(torch.cat([h, self.aggregate(h)], dim=1))
+
+
+class GIN2(nn.Module):
+    """GIN: h' = MLP((1 + eps) h + A h) with two-layer bias-free MLPs and learnable eps, raw
+    adjacency A (GINBench, gnn_bench/router_vs_baselines_gin.py:47-74)."""
+
+    def __init__(self, in_dim: int, hidden: int, out_dim: int, spmm: Callable,
+                 spmm_t: Optional[Callable] = None, sharding: Optional[RowSharding] = None,
+                 operand_format: Optional[Callable] = None, operand_format_t: Optional[Callable] = None,
+                 panels: int = 1):
+        super().__init__()
+        self.eps1 = nn.Parameter(torch.zeros(1))
+        self.eps2 = nn.Parameter(torch.zeros(1))
+        self.mlp1 = nn.Sequential(nn.Linear(in_dim, hidden, bias=False), nn.ReLU(), nn.Linear(hidden, hidden, bias=False))
+        self.mlp2 = nn.Sequential(nn.Linear(hidden, hidden, bias=False), nn.ReLU(), nn.Linear(hidden, out_dim, bias=False))
+        _attach(self, spmm, spmm_t, sharding, operand_format, operand_format_t, panels)
+
+    def forward(self, X_local):
+        h = F.relu(self.mlp1((1.0 + self.eps1) * X_local + self.aggregate(X_local)))
+        return self.mlp2((1.0 + self.eps2) * h + self.aggregate(h))
+
+
+def train_step(model, opt, X_local, y_local, total_rows: int):
     """zero_grad -> forward -> cross-entropy (mean over ALL rows) -> backward ->
     all-reduce of the weight gradients -> optimizer step. Returns the global loss."""
     sh = model.sharding

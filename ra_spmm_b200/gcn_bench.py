@@ -23,7 +23,7 @@ from . import partition as P
 from .gcn import GCN2, GraphOperator, RowSharding, train_step
 
 
-def main():
+def parse_args(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--scale", type=float, default=1.0)
     ap.add_argument("--kernel", default="routed")
@@ -35,19 +35,22 @@ def main():
     ap.add_argument("--gather", default="kernel", choices=["kernel", "fp32"],
                     help="multi-GPU: all-gather the row slabs in the format the kernel reads (fp16, padded, "
                          "for the FP16 tile paths) or as fp32")
-    args = ap.parse_args()
-    world = int(os.environ.get("WORLD_SIZE", "1")); rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
-            os.environ["NCCL_DEBUG"] = "WARN"
-        dist.init_process_group("nccl", device_id=dev)
+    ap.add_argument("--panels", type=int, default=1,
+                    help="multi-GPU: gather wide operands in this many column panels and start each panel's "
+                         "SpMM when its own gather has landed")
+    return ap.parse_args(argv)
 
-    n = max(2000, int(2_449_029 * args.scale))
-    a = G.gcn_normalized_sbm(n=n, n_comm=max(2, int(500 * args.scale)), mean_degree=50.0, seed=123)
+
+def measure(args, world: int, rank: int, dev):
+    """Times the step on an initialised process group; returns the result line on rank 0, else None."""
+    if world > 1:
+        if rank == 0:
+            a, _, _ = G.cached_config("C5", args.scale)
+        dist.barrier()
+        if rank != 0:
+            a, _, _ = G.cached_config("C5", args.scale)
+    else:
+        a, _, _ = G.cached_config("C5", args.scale)
     bounds = P.nnz_balanced_row_splits(a.rowptr, world)
     r0, r1 = int(bounds[rank]), int(bounds[rank + 1])
     rp, ci, va = P.row_block(a.rowptr, a.colind, a.vals, r0, r1)
@@ -59,7 +62,8 @@ def main():
     y = torch.randint(0, 47, (a.M,), generator=g)[r0:r1].to(dev)
     torch.manual_seed(123)
     model = GCN2(100, 256, 47, op.matmul, sharding=sharding,
-                 operand_format=op.operand_format if args.gather == "kernel" else None).to(dev)
+                 operand_format=op.operand_format if args.gather == "kernel" else None,
+                 panels=args.panels).to(dev)
     opt = torch.optim.Adam(model.parameters(), lr=1e-2)
 
     for _ in range(max(args.warmup, 1)):
@@ -95,6 +99,7 @@ def main():
         torch.cuda.synchronize()
         spmm_ms = {"step_ms": s0.elapsed_time(s1),
                    "spmm_calls": [{"N": n, "dtype": dt, "ms": e0.elapsed_time(e1)} for n, dt, e0, e1 in calls]}
+    line = None
     if rank == 0:
         nnz = a.nnz
         spmm_flops = 2.0 * nnz * (256 + 47) * 2            # forward + backward of the two SpMM sites
@@ -103,7 +108,8 @@ def main():
                 "spmm_gflops": spmm_flops / (ms * 1e-3) / 1e9, "loss": float(loss),
                 "config": {"workload": f"2-layer GCN on SBM {a.M} nodes, nnz {nnz}, 100->256->47", "kernel": args.kernel,
                            "labels": op.labels, "allgather_bytes_per_step_per_rank": sharding.comm_bytes // args.steps,
-                           "partition": f"{world} nnz-balanced row blocks, all-gather before each SpMM", "gather": args.gather}}
+                           "partition": f"{world} nnz-balanced row blocks, all-gather before each SpMM", "gather": args.gather,
+                           "panels": args.panels}}
         if spmm_ms is not None:
             line["breakdown"] = spmm_ms
         if args.cpu_baseline and world == 1:
@@ -117,6 +123,24 @@ def main():
             t0 = time.perf_counter(); train_step(cm, co, Xc, yc, a.M); t_cpu = time.perf_counter() - t0
             line["cpu_baseline"] = {"value": t_cpu * 1e3, "unit": "ms", "cores": os.cpu_count(),
                                     "kind": "reference", "sample": "one full step, torch.sparse.mm CPU"}
+    del model, opt, op
+    torch.cuda.empty_cache()
+    return line
+
+
+def main():
+    args = parse_args()
+    world = int(os.environ.get("WORLD_SIZE", "1")); rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"
+        dist.init_process_group("nccl", device_id=dev)
+    line = measure(args, world, rank, dev)
+    if rank == 0:
         print(json.dumps(line))
     if world > 1:
         dist.barrier()

@@ -22,13 +22,18 @@ def main():
     ap.add_argument("--kernel", default="routed")
     ap.add_argument("--scale", type=float, default=1.0)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--f32-b", action="store_true", help="hand B over as fp32 even when the configuration's B is fp16")
     args = ap.parse_args()
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
-    a, N, b_dtype = G.make_config(args.config, args.scale)
-    B = G.dense(a.K, N, G.CONFIG_SEEDS[args.config], b_dtype).float().to(dev)
+    a, N, b_dtype = G.cached_config(args.config, args.scale)
+    B = G.dense(a.K, N, G.CONFIG_SEEDS[args.config], b_dtype).to(dev)
+    if args.f32_b or b_dtype == "float32":
+        B = B.float()
     rp, ci, va = a.torch(dev)
     kernel = args.kernel
+    if kernel.endswith("_TF32") or kernel in ("CSR_DIRECT", "ZERO_OVERHEAD_CSR"):
+        B = B.float()
     if kernel == "routed":
         from . import ra_spmm
         d = ra_spmm.make_router_plan(rp, ci, va, a.M, a.K, N)

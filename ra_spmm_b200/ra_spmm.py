@@ -36,6 +36,7 @@ __all__ = [
     "spmm_cusparse", "spmm_cusparse_fp16", "make_cusparse_plan", "run_cusparse_plan",
     "benchmark_cusparse", "benchmark_cusparse_cold", "benchmark_cusparse_fp16", "benchmark_cusparse_fp16_cold",
     "RAZeroOverheadPlan", "RATcDirectPlan", "RACommunityTCPlan", "RASegmentHybridPlan",
+    "save_plan", "load_zero_overhead_plan", "load_tile_plan",
 ]
 
 
@@ -381,6 +382,39 @@ def run_segment_hybrid_plan(plan, colind, vals, B):
 
 def run_segment_hybrid_plan_tf32(plan, colind, vals, B):
     return _run_tile_plan(plan, B, _capi.PRECISION_TF32, "SegmentHybrid")
+
+
+# ---------------------------------------------------------------------------
+# Plan files (no counterpart in the reference, whose plans live in one process only):
+# every array with its length and FNV-1a checksum, verified again on load.
+# ---------------------------------------------------------------------------
+def save_plan(plan, path) -> None:
+    """Write a ZERO_OVERHEAD_CSR or tile plan to `path`."""
+    fn = _lib().ra_zo_plan_save if isinstance(plan, RAZeroOverheadPlan) else _lib().ra_tile_plan_save
+    with torch.cuda.device(plan._device):
+        _capi.check(fn(plan._h, os.fsencode(path)), "save_plan")
+
+
+def load_zero_overhead_plan(path, device=None) -> "RAZeroOverheadPlan":
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    handle = C.c_void_p()
+    with torch.cuda.device(dev):
+        _capi.check(_lib().ra_zo_plan_load(os.fsencode(path), C.byref(handle)), "load_zero_overhead_plan")
+    return RAZeroOverheadPlan(handle.value, dev)
+
+
+def load_tile_plan(path, device=None):
+    """Plan object of the family stored in the file (RATcDirectPlan, RACommunityTCPlan or
+    RASegmentHybridPlan)."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    handle = C.c_void_p()
+    with torch.cuda.device(dev):
+        _capi.check(_lib().ra_tile_plan_load(os.fsencode(path), C.byref(handle)), "load_tile_plan")
+    info = _capi.RaTileInfo()
+    _capi.check(_lib().ra_tile_plan_info(handle.value, C.byref(info)), "ra_tile_plan_info")
+    cls = {_capi.TILE_COMMUNITY_TC: RACommunityTCPlan, _capi.TILE_SEGMENT_HYBRID: RASegmentHybridPlan}.get(
+        info.kind, RATcDirectPlan)
+    return cls(handle.value, dev)
 
 
 # ---------------------------------------------------------------------------

@@ -65,6 +65,42 @@ want = cpu_op(rp, sh.remap_columns(ci), va, sh.gathered_rows)(sh.all_gather_rows
 assert seen["dtype"] == torch.float16 and seen["width"] == 48, seen
 assert got.shape == (r1 - r0, 47) and torch.equal(got, want)
 
+# ---- panelled gather: 4 column panels of a 128-wide operand, each gathered on its own ----
+H = torch.randn(r1 - r0, 128, generator=torch.Generator().manual_seed(200 + rank))
+op = cpu_op(rp, sh.remap_columns(ci), va, sh.gathered_rows)
+whole = sharded_spmm(H, op, op, sh)
+in_panels = sharded_spmm(H, op, op, sh, panels=4)
+assert torch.allclose(whole, in_panels, rtol=1e-6, atol=1e-6)
+assert torch.equal(sharded_spmm(H[:, :40].contiguous(), op, op, sh, panels=4),      # too narrow: falls back to one gather
+                   sharded_spmm(H[:, :40].contiguous(), op, op, sh))
+
+# ---- GraphSAGE (row-mean operator, not symmetric: the backward needs the transposed row block)
+# and GIN (raw adjacency, learnable eps) against the unsharded step ----
+from ra_spmm_b200.gcn import GIN2, SAGE2, aggregation_operator, transpose_csr   # noqa: E402
+raw = G.chung_lu_power_law(n=1500, seed=5)                                       # structure only
+for name, cls in (("sage", SAGE2), ("gin", GIN2)):
+    orp, oci, ova = aggregation_operator(raw.rowptr, raw.colind, raw.M, name)
+    trp, tci, tva = transpose_csr(orp, oci, ova, raw.M, raw.K)
+    torch.manual_seed(11)
+    Xs = torch.randn(raw.M, 24)
+    ys = torch.randint(0, 7, (raw.M,))
+    torch.manual_seed(3)
+    ref = cls(24, 32, 7, cpu_op(orp, oci, ova, raw.K), cpu_op(trp, tci, tva, raw.M), sharding=RowSharding([0, raw.M]))
+    ref_loss = train_step(ref, torch.optim.Adam(ref.parameters(), lr=1e-2), Xs, ys, raw.M)
+    b = P.nnz_balanced_row_splits(orp, world)
+    q0, q1 = int(b[rank]), int(b[rank + 1])
+    shs = RowSharding(b, rank, world)
+    frp, fci, fva = P.row_block(orp, oci, ova, q0, q1)
+    brp, bci, bva = P.row_block(trp, tci, tva, q0, q1)
+    torch.manual_seed(3)
+    mdl = cls(24, 32, 7, cpu_op(frp, shs.remap_columns(fci), fva, shs.gathered_rows),
+              cpu_op(brp, shs.remap_columns(bci), bva, shs.gathered_rows), sharding=shs)
+    loss = train_step(mdl, torch.optim.Adam(mdl.parameters(), lr=1e-2), Xs[q0:q1], ys[q0:q1], raw.M)
+    assert abs(float(loss) - float(ref_loss)) < 1e-5, (name, float(loss), float(ref_loss))
+    for pa, pb in zip(mdl.parameters(), ref.parameters()):
+        assert torch.allclose(pa.grad, pb.grad, rtol=1e-4, atol=1e-6), name
+        assert torch.allclose(pa, pb, rtol=1e-4, atol=1e-6), name
+
 ok = torch.tensor([1]); dist.all_reduce(ok)
 if rank == 0 and int(ok) == world:
     print("GCN_GLOO_OK")

@@ -67,3 +67,20 @@ def test_plan_checksum_hook_prints_fnv1a_per_array(monkeypatch, capsys):
     want = fnv1a64(np.array([1, 2, 3], dtype=np.int32))
     assert err.startswith("[RA_PLAN_CHECKSUM] FakePlan ")
     assert f"a={want:016x}" in err and "none=cbf29ce484222325" in err and " all=" in err
+
+
+def test_plan_file_errors_come_before_any_device_work(lib, tmp_path):
+    """Header checks of the plan-file readers (no GPU needed: they fail before the first allocation)."""
+    out = C.c_void_p()
+    assert lib.ra_tile_plan_load(str(tmp_path / "missing.plan").encode(), C.byref(out)) == 1
+    assert b"cannot open" in lib.ra_last_error_string() and not out.value
+    bad = tmp_path / "bad.plan"
+    bad.write_bytes(b"NOTAPLAN" + bytes(200))
+    assert lib.ra_zo_plan_load(str(bad).encode(), C.byref(out)) == 1
+    assert b"bad magic" in lib.ra_last_error_string()
+    bad.write_bytes(b"RASPMMB2" + (7).to_bytes(4, "little") + bytes(200))
+    assert lib.ra_zo_plan_load(str(bad).encode(), C.byref(out)) == 3          # RA_ERR_UNSUPPORTED: version
+    bad.write_bytes(b"RASPMMB2" + (1).to_bytes(4, "little") + (1).to_bytes(4, "little") + bytes(16 * 8))
+    assert lib.ra_zo_plan_load(str(bad).encode(), C.byref(out)) == 1          # a tile file given to the ZERO_OVERHEAD reader
+    assert b"tile" in lib.ra_last_error_string()
+    assert lib.ra_zo_plan_save(None, b"x") == 1

@@ -343,6 +343,7 @@ def test_a_wait_that_runs_out_is_reported_and_the_plan_stays_usable(cuda, monkey
     assert plan.device_status() == 0
     monkeypatch.setenv("RA_TILE_TMA", "1")
     monkeypatch.setenv("RA_TILE_TC5", "0")
+    monkeypatch.setenv("RA_TILE_G4", "0")
     assert rel_fro(ra_spmm.run_tc_direct_plan(plan, B), want.cpu().numpy()) < 1e-6     # the ring itself works
     assert plan.device_status() == 0
     monkeypatch.setenv("RA_TILE_TMA_POLL_LIMIT", "0")
