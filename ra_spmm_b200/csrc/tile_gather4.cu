@@ -36,11 +36,40 @@ namespace ra {
 constexpr int kG4AtomBytes = 1024;      // 8 rows x 128 bytes
 constexpr int kG4ValBytes  = 128;     // packed values of a block in the plan
 
+// L2 eviction policies. The plan (packed values + gather indices, 160 bytes per block) is a
+// stream that is read once per SpMM and is several times larger than the L2; the rows of B
+// are what the L2 can serve again. The stream is therefore loaded evict-first and the rows of B
+// evict-last, and C is written with streaming stores.
+__device__ __forceinline__ unsigned long long l2_policy_evict_first() {
+    unsigned long long p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ unsigned long long l2_policy_normal() {
+    unsigned long long p;
+    asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ unsigned long long l2_policy_evict_last() {
+    unsigned long long p;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+
 __device__ __forceinline__ void tma_gather4(unsigned dst, const CUtensorMap* map, int x,
-                                            int r0, int r1, int r2, int r3, unsigned mbar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cta.global.tile::gather4.mbarrier::complete_tx::bytes "
-                 "[%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
-                 :: "r"(dst), "l"(map), "r"(x), "r"(r0), "r"(r1), "r"(r2), "r"(r3), "r"(mbar) : "memory");
+                                            int r0, int r1, int r2, int r3, unsigned mbar,
+                                            unsigned long long policy) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes.L2::cache_hint "
+                 "[%0], [%1, {%2, %3, %4, %5, %6}], [%7], %8;"
+                 :: "r"(dst), "l"(map), "r"(x), "r"(r0), "r"(r1), "r"(r2), "r"(r3), "r"(mbar), "l"(policy) : "memory");
+}
+__device__ __forceinline__ void bulk_copy_g2s_hint(unsigned dst, const void* src, unsigned bytes, unsigned mbar,
+                                                   unsigned long long policy) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+                 :: "r"(dst), "l"(src), "r"(bytes), "r"(mbar), "l"(policy) : "memory");
+}
+__device__ __forceinline__ int4 ld_stream_first_int4(const int4* p) {      // read-once data: evict first
+    return __ldcs(p);
 }
 
 // shared-memory row of tensor-core k index j (see the header comment)
@@ -51,7 +80,7 @@ __device__ __forceinline__ int g4_row_of_k(int j) { return (j < 4) ? 2 * j : 2 *
 template <bool kTF32, int kMode, int S, int D>
 __global__ void __launch_bounds__(256)
 tile_spmm_gather4_kernel(const __grid_constant__ CUtensorMap bmap, TileArgs a, int slices_total,
-                         int warps_per_group, int groups_total, int* __restrict__ status, unsigned wait_hint_ns)
+                         int warps_per_group, int groups_total, int* __restrict__ status, unsigned wait_hint_ns, int l2_policies)
 {
     constexpr int kMT    = kTF32 ? 2 : 4;           // 16-feature MMA tiles per slice
     constexpr int kElem  = kTF32 ? 4 : 2;
@@ -111,10 +140,12 @@ tile_spmm_gather4_kernel(const __grid_constant__ CUtensorMap bmap, TileArgs a, i
     int ibase = 0;
     auto load_batch = [&](int first, int4& x, int4& y) {
         const int blk = first + lane;
-        if (blk < nb) { x = __ldg(atox4 + 2 * blk); y = __ldg(atox4 + 2 * blk + 1); }
+        if (blk < nb) { x = ld_stream_first_int4(atox4 + 2 * blk); y = ld_stream_first_int4(atox4 + 2 * blk + 1); }
     };
     load_batch(0, ca, cb);
     load_batch(32, na, nb4);
+    const unsigned long long pol_stream = l2_policies ? l2_policy_evict_first() : l2_policy_normal();
+    const unsigned long long pol_rows = l2_policies ? l2_policy_evict_last() : l2_policy_normal();
 
     auto fetch = [&](int rf) {                                   // rf: block index relative to B0
         if (rf >= ibase + 32) { ca = na; cb = nb4; ibase += 32; load_batch(ibase + 32, na, nb4); }
@@ -128,12 +159,12 @@ tile_spmm_gather4_kernel(const __grid_constant__ CUtensorMap bmap, TileArgs a, i
                 if (sl < s_valid) {
                     // rows 0-3 of the atom = vectors 0,4,1,5; rows 4-7 = vectors 2,6,3,7
                     const int x = (slice0 + sl) * kSlcF;         // element offset of the slice in a B row
-                    tma_gather4(dst + (unsigned)(sl * kG4AtomBytes), &bmap, x, ca.x, cb.x, ca.y, cb.y, bar);
-                    tma_gather4(dst + (unsigned)(sl * kG4AtomBytes + 512), &bmap, x, ca.z, cb.z, ca.w, cb.w, bar);
+                    tma_gather4(dst + (unsigned)(sl * kG4AtomBytes), &bmap, x, ca.x, cb.x, ca.y, cb.y, bar, pol_rows);
+                    tma_gather4(dst + (unsigned)(sl * kG4AtomBytes + 512), &bmap, x, ca.z, cb.z, ca.w, cb.w, bar, pol_rows);
                 }
             }
-            bulk_copy_g2s(vals_s + (unsigned)(st * kG4ValBytes), vals_base + (size_t)rf * kG4ValBytes,
-                          (unsigned)kG4ValBytes, bar);
+            bulk_copy_g2s_hint(vals_s + (unsigned)(st * kG4ValBytes), vals_base + (size_t)rf * kG4ValBytes,
+                               (unsigned)kG4ValBytes, bar, pol_stream);
         }
     };
 
@@ -273,11 +304,11 @@ tile_spmm_gather4_kernel(const __grid_constant__ CUtensorMap bmap, TileArgs a, i
                 const int n = f0 + s * kSlcF + 4 * g;
                 if (s < s_valid && n < N) {
                     if (dst_row_lo >= 0)
-                        *reinterpret_cast<float4*>(cbase + (size_t)dst_row_lo * N + n) =
-                            make_float4(acc[s][0][0], acc[s][0][2], acc[s][1][0], acc[s][1][2]);
+                        st_stream_float4(reinterpret_cast<float4*>(cbase + (size_t)dst_row_lo * N + n),
+                                         make_float4(acc[s][0][0], acc[s][0][2], acc[s][1][0], acc[s][1][2]));
                     if (dst_row_hi >= 0)
-                        *reinterpret_cast<float4*>(cbase + (size_t)dst_row_hi * N + n) =
-                            make_float4(acc[s][0][1], acc[s][0][3], acc[s][1][1], acc[s][1][3]);
+                        st_stream_float4(reinterpret_cast<float4*>(cbase + (size_t)dst_row_hi * N + n),
+                                         make_float4(acc[s][0][1], acc[s][0][3], acc[s][1][1], acc[s][1][3]));
                 }
             }
         } else {
@@ -290,13 +321,13 @@ tile_spmm_gather4_kernel(const __grid_constant__ CUtensorMap bmap, TileArgs a, i
                         const bool c0 = n < N, c1 = n + 8 < N;   // padded operand columns are not stored
                         if (dst_row_lo >= 0) {
                             float* r = cbase + (size_t)dst_row_lo * N + n;
-                            if (c0) r[0] = acc[s][t][0];
-                            if (c1) r[8] = acc[s][t][2];
+                            if (c0) st_stream_float(r, acc[s][t][0]);
+                            if (c1) st_stream_float(r + 8, acc[s][t][2]);
                         }
                         if (dst_row_hi >= 0) {
                             float* r = cbase + (size_t)dst_row_hi * N + n;
-                            if (c0) r[0] = acc[s][t][1];
-                            if (c1) r[8] = acc[s][t][3];
+                            if (c0) st_stream_float(r, acc[s][t][1]);
+                            if (c1) st_stream_float(r + 8, acc[s][t][3]);
                         }
                     }
                 }
@@ -372,13 +403,17 @@ static int launch_g4(const CUtensorMap& map, const TileArgs& a, int slices_total
     }));
     const long long weight = a.total_blocks + a.num_units;
     const int ctas_per_sm = (int)std::max<size_t>(1, std::min<size_t>(16, (220 * 1024) / (smem + 1024)));
-    const int waves = std::max(1, env_int("RA_G4_WAVES", 3));
+    // groups per resident slot: the FP16 path on windows (even unit lengths) is fastest with one
+    // range per resident group (C3 4.8 vs 5.1 ms); TF32 and the segment lists, whose ranges differ
+    // more in cost, with three
+    const int waves = std::max(1, env_int("RA_G4_WAVES", (!kTF32 && kMode != 2) ? 1 : 3));
     long long groups = (long long)sm_count() * ctas_per_sm * groups_per_cta * waves;
     groups = std::min(groups, std::max<long long>(1, weight / 48));
     const int ctas = (int)((groups + groups_per_cta - 1) / groups_per_cta);
     groups = (long long)ctas * groups_per_cta;
     kern<<<ctas, warps * 32, smem, st>>>(map, a, slices_total, wpg, (int)groups, status,
-                                         (unsigned)std::max(0, env_int("RA_G4_WAIT_HINT_NS", 0)));
+                                         (unsigned)std::max(0, env_int("RA_G4_WAIT_HINT_NS", 0)),
+                                         env_int("RA_G4_L2POLICY", 1));
     RA_KERNEL_CHECK();
     return RA_OK;
 }

@@ -902,6 +902,44 @@ tile_merge_kernel(const int* __restrict__ split_wins, const int* __restrict__ sp
     }
 }
 
+// Same merge for N % 4 == 0 and 16-byte aligned C / scratch: one thread sums a float4 column
+// group, four partial tiles in flight at a time (the partials of a hub window are 8 x N floats
+// 8*N floats apart, so the loads of one thread are independent); the additions stay in
+// ascending slot order, as in the scalar kernel.
+__global__ void __launch_bounds__(256)
+tile_merge_vec4_kernel(const int* __restrict__ split_wins, const int* __restrict__ split_off,
+                       const float4* __restrict__ scratch, float4* __restrict__ C,
+                       int num_split, int M, int N4)
+{
+    const long long total = (long long)num_split * kWindowRows * N4;
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (long long)gridDim.x * blockDim.x) {
+        const int sw = (int)(idx / ((long long)kWindowRows * N4));
+        const long long rem = idx - (long long)sw * kWindowRows * N4;
+        const int slot = (int)(rem / N4);
+        const int col = (int)(rem - (long long)slot * N4);
+        const int r = __ldg(split_wins + sw) * kWindowRows + slot;
+        if (r >= M) continue;
+        const int o_begin = __ldg(split_off + sw), o_end = __ldg(split_off + sw + 1);
+        const long long stride = (long long)kWindowRows * N4;
+        const float4* src = scratch + ((long long)o_begin * kWindowRows + slot) * N4 + col;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        int o = o_begin;
+        for (; o + 4 <= o_end; o += 4, src += 4 * stride) {
+            const float4 p0 = __ldcs(src), p1 = __ldcs(src + stride), p2 = __ldcs(src + 2 * stride), p3 = __ldcs(src + 3 * stride);
+            acc.x += p0.x; acc.y += p0.y; acc.z += p0.z; acc.w += p0.w;
+            acc.x += p1.x; acc.y += p1.y; acc.z += p1.z; acc.w += p1.w;
+            acc.x += p2.x; acc.y += p2.y; acc.z += p2.z; acc.w += p2.w;
+            acc.x += p3.x; acc.y += p3.y; acc.z += p3.z; acc.w += p3.w;
+        }
+        for (; o < o_end; ++o, src += stride) {
+            const float4 p = __ldcs(src);
+            acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
+        }
+        C[(long long)r * N4 + col] = acc;
+    }
+}
+
 // B fp32 -> fp16, round to nearest even (replaces convert_b_to_half_kernel,
 // tc/ra_tc_direct.cu:85-104): 8 elements per thread, 2x128-bit in, 128-bit out.
 __global__ void __launch_bounds__(256)
@@ -973,7 +1011,10 @@ static int launch_tile(const TileArgs& a, const void* B, bool staged, cudaStream
         // a warp of the TMA ring has at most three blocks in flight, so it walks one unit slower than
         // a warp of the 8-stage cp.async ring: units of thousands of blocks (hub windows of TC_DIRECT /
         // COMMUNITY_TC on power-law graphs) stay on the cp.async ring
-        const bool g4_auto = !use_tc5 && a.max_unit_blocks <= 1024;
+        // rows that are not whole 128-byte slices (the 47-class GCN output, padded to 48 halves)
+        // straddle the TMA boxes and measured slower there (4.9 vs 3.6 ms)
+        const bool g4_auto = !use_tc5 && a.max_unit_blocks <= 1024 && (kMode == 2 || !kTF32 || a.N >= 256) &&
+                             (a.ldb * elem) % 128 == 0;
         const bool use_g4 = !kZC && (g4_env ? (g4_env[0] == '1') : g4_auto);
         if (use_g4) {
             const int rc = launch_tile_gather4<kTF32, kMode>(a, B, a.K, st, status);
@@ -1129,10 +1170,18 @@ extern "C" int ra_tile_plan_run(RaTilePlan* p, int precision, const void* d_B, i
     if (rc != RA_OK) return rc;
 
     if (p->kind == RA_TILE_SEGMENT_HYBRID && p->num_split_windows > 0) {
-        const long long total = (long long)p->num_split_windows * kWindowRows * N;
-        const int blocks = (int)std::min<long long>((total + 255) / 256, (long long)sm_count() * 16);
-        tile_merge_kernel<<<std::max(blocks, 1), 256, 0, st>>>(p->d_split_wins, p->d_split_off, p->d_scratch,
-                                                               d_C, p->num_split_windows, p->M, N);
+        if (N % 4 == 0 && aligned16(d_C) && aligned16(p->d_scratch)) {
+            const long long total = (long long)p->num_split_windows * kWindowRows * (N / 4);
+            const int blocks = (int)std::min<long long>((total + 255) / 256, (long long)sm_count() * 16);
+            tile_merge_vec4_kernel<<<std::max(blocks, 1), 256, 0, st>>>(
+                p->d_split_wins, p->d_split_off, reinterpret_cast<const float4*>(p->d_scratch),
+                reinterpret_cast<float4*>(d_C), p->num_split_windows, p->M, N / 4);
+        } else {
+            const long long total = (long long)p->num_split_windows * kWindowRows * N;
+            const int blocks = (int)std::min<long long>((total + 255) / 256, (long long)sm_count() * 16);
+            tile_merge_kernel<<<std::max(blocks, 1), 256, 0, st>>>(p->d_split_wins, p->d_split_off, p->d_scratch,
+                                                                   d_C, p->num_split_windows, p->M, N);
+        }
         RA_KERNEL_CHECK();
     }
     return RA_OK;

@@ -21,7 +21,6 @@
 // The reference adds multi-chunk partials with fp32 atomicAdd in arbitrary
 // order; here the merge order is fixed, so results are run-to-run identical.
 #include "csr_engine.cuh"
-#include "csr_chunk.cuh"
 #include "csr_stream.cuh"
 #include "scan.cuh"
 #include "zo_plan.cuh"
@@ -174,34 +173,49 @@ zo_chunk_generic_kernel(const int* __restrict__ rowptr, const int* __restrict__ 
     }
 }
 
-// One warp per listed row: C[row,:] = sum of its scratch slots, ascending.
+// Listed rows (empty rows and multi-chunk rows): C[row,:] = sum of the row's scratch slots in
+// ascending chunk order (no slots = an empty row = zeros). vec4: one thread per float4 of a row,
+// so a 64-wide row takes 16 threads and a warp covers two rows; two slots in flight per thread.
 __global__ void __launch_bounds__(kZoThreads)
 zo_finish_kernel(const int* __restrict__ zero_ids, const int* __restrict__ zero_slot_off,
                  const float* __restrict__ scratch, float* __restrict__ C,
                  int num_zero, int N, int vec4)
 {
-    const int lane = threadIdx.x & 31;
-    const i64 z = ((i64)blockIdx.x * kZoThreads + threadIdx.x) >> 5;
-    if (z >= num_zero) return;
-    const int row = __ldg(zero_ids + z);
-    const int o0 = __ldg(zero_slot_off + z);
-    const int o1 = __ldg(zero_slot_off + z + 1);
     if (vec4) {
         const int N4 = N >> 2;
-        float4* dst = reinterpret_cast<float4*>(C + (i64)row * N);
-        for (int n4 = lane; n4 < N4; n4 += 32) {
+        const i64 total = (i64)num_zero * N4;
+        const float4* s4 = reinterpret_cast<const float4*>(scratch);
+        for (i64 idx = (i64)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (i64)gridDim.x * blockDim.x) {
+            const int z = (int)(idx / N4);
+            const int n4 = (int)(idx - (i64)z * N4);
+            const int row = __ldg(zero_ids + z);
+            const int o0 = __ldg(zero_slot_off + z);
+            const int o1 = __ldg(zero_slot_off + z + 1);
             float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (int o = o0; o < o1; ++o) {
-                const float4 p = reinterpret_cast<const float4*>(scratch + (i64)o * N)[n4];
+            int o = o0;
+            for (; o + 2 <= o1; o += 2) {
+                const float4 p = __ldcs(s4 + (i64)o * N4 + n4), q = __ldcs(s4 + (i64)(o + 1) * N4 + n4);
+                acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
+                acc.x += q.x; acc.y += q.y; acc.z += q.z; acc.w += q.w;
+            }
+            if (o < o1) {
+                const float4 p = __ldcs(s4 + (i64)o * N4 + n4);
                 acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
             }
-            st_stream_float4(dst + n4, acc);
+            st_stream_float4(reinterpret_cast<float4*>(C + (i64)row * N) + n4, acc);
         }
     } else {
-        for (int n = lane; n < N; n += 32) {
-            float acc = 0.f;
-            for (int o = o0; o < o1; ++o) acc += scratch[(i64)o * N + n];
-            C[(i64)row * N + n] = acc;
+        const int lane = threadIdx.x & 31;
+        const i64 warps = ((i64)gridDim.x * kZoThreads) >> 5;
+        for (i64 z = ((i64)blockIdx.x * kZoThreads + threadIdx.x) >> 5; z < num_zero; z += warps) {
+            const int row = __ldg(zero_ids + z);
+            const int o0 = __ldg(zero_slot_off + z);
+            const int o1 = __ldg(zero_slot_off + z + 1);
+            for (int n = lane; n < N; n += 32) {
+                float acc = 0.f;
+                for (int o = o0; o < o1; ++o) acc += scratch[(i64)o * N + n];
+                C[(i64)row * N + n] = acc;
+            }
         }
     }
 }
@@ -366,30 +380,14 @@ int zo_run_with_scratch(const RaZoPlan* p, float* scratch, const int* d_rowptr,
     RaZoPlan view = *p;            // shallow copy that carries the scratch pointer
     view.d_scratch = scratch;
     // RA_ZO_CHUNK_ENGINE=register runs the chunks on the register engine (diagnostic switch)
+    // RA_ZO_CHUNK_ENGINE=register runs the chunks on the register engine (diagnostic switch)
     const char* engine_env = std::getenv("RA_ZO_CHUNK_ENGINE");
-    const std::string engine = engine_env ? engine_env : "";
-    const bool chunk_register = engine == "register";
-    // RA_ZO_CHUNK_ENGINE=lean: the chunks run on the short-path chunk kernel (csr_chunk.cuh) and the
-    // small rows follow in their own launch
-    const bool chunk_lean = engine == "lean" && wide_ok && stream_aligned_width_ok(N);
-    const bool chunk_reg2 = engine == "reg2" && wide_ok && stream_aligned_width_ok(N);
+    const bool chunk_register = engine_env && std::string(engine_env) == "register";
     // A matrix made of long rows (nearly all work in chunks) at N >= 256 runs faster on the
     // register engine, as CSR_DIRECT does there: full chunks keep enough loads in flight and
     // every gathered byte crosses the shared-memory data path once.
     const bool long_rows = N >= 256 && (long long)p->num_chunks >= 16ll * p->num_small;
     const bool chunk_stream = wide_ok && stream_aligned_width_ok(N) && !chunk_register && !long_rows;
-    if (p->num_chunks > 0 && (phase_mask & 1) && chunk_reg2) {
-        const int rc = launch_zo_chunks_reg(d_rowptr, d_colind, d_vals, d_B, d_C, scratch, p->d_chunk_rows,
-                                            p->d_chunk_starts, p->d_chunk_slot, p->num_chunks, N, st);
-        if (rc != RA_OK) return rc;
-        phase_mask &= ~1;
-    }
-    if (p->num_chunks > 0 && (phase_mask & 1) && chunk_lean) {
-        const int rc = launch_zo_chunks_lean(d_rowptr, d_colind, d_vals, d_B, d_C, scratch, p->d_chunk_rows,
-                                             p->d_chunk_starts, p->d_chunk_slot, p->num_chunks, N, st);
-        if (rc != RA_OK) return rc;
-        phase_mask &= ~1;
-    }
     if (p->num_chunks > 0 && p->num_small > 0 && (phase_mask & 3) == 3 && chunk_stream) {
         // chunks and small rows in one launch: the chunk warps (the long items) start first
         StreamArgs a{};
@@ -428,10 +426,11 @@ int zo_run_with_scratch(const RaZoPlan* p, float* scratch, const int* d_rowptr,
         if (rc != RA_OK) return rc;
     }
     if (p->num_zero_rows > 0 && (phase_mask & 4)) {
-        const int blocks = (int)(((i64)p->num_zero_rows * 32 + kZoThreads - 1) / kZoThreads);
+        const int vec4 = (N % 4 == 0 && aligned16(d_C) && aligned16(scratch)) ? 1 : 0;
+        const i64 threads = vec4 ? (i64)p->num_zero_rows * (N / 4) : (i64)p->num_zero_rows * 32;
+        const int blocks = (int)std::max<i64>(1, std::min<i64>((threads + kZoThreads - 1) / kZoThreads, (i64)sm_count() * 32));
         zo_finish_kernel<<<blocks, kZoThreads, 0, st>>>(
-            p->d_zero_row_ids, p->d_zero_slot_off, scratch, d_C, p->num_zero_rows, N,
-            (N % 4 == 0 && aligned16(d_C) && aligned16(scratch)) ? 1 : 0);
+            p->d_zero_row_ids, p->d_zero_slot_off, scratch, d_C, p->num_zero_rows, N, vec4);
         RA_KERNEL_CHECK();
     }
     return RA_OK;
