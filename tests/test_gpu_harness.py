@@ -43,6 +43,26 @@ def test_cusparse_passthrough_matches(graph):
     assert float((C - Cc).norm() / Cc.norm()) < 1e-5
 
 
+def test_cusparse_benchmark_passthroughs_have_the_reference_dict_shape(graph):
+    """benchmark_cusparse / _cold / _fp16 / _fp16_cold (bindings/ra_bindings.cpp:838-1037): keys the sweep
+    driver reads (ra_real_graph_eval.py:540-560) and a sane precision-matched product."""
+    a, rp, ci, va, B = graph
+    warm = ra_spmm.benchmark_cusparse(rp, ci, va, B, warmup=1, iters=2)
+    cold = ra_spmm.benchmark_cusparse_cold(rp, ci, va, B, 1)
+    w16 = ra_spmm.benchmark_cusparse_fp16(rp, ci, va, B, warmup=1, iters=2)
+    c16 = ra_spmm.benchmark_cusparse_fp16_cold(rp, ci, va, B, 1)
+    for d, path in ((warm, "CUSPARSE"), (cold, "CUSPARSE"), (w16, "CUSPARSE_FP16"), (c16, "CUSPARSE_FP16")):
+        assert {"plan_ms", "exec_ms", "total_ms", "gflops", "path", "preprocess_ms", "cusparse_algorithm",
+                "in_main_portfolio", "legacy_baseline", "external_baseline"} <= set(d)
+        assert d["path"] == path and d["exec_ms"] > 0 and d["total_ms"] >= d["exec_ms"]
+    assert warm["plan_ms"] == 0 and cold["plan_ms"] > 0 and cold["in_main_portfolio"] and not w16["in_main_portfolio"]
+    C = ra_spmm.spmm_csr_direct(rp, ci, va, B)
+    C16 = ra_spmm.spmm_cusparse_fp16(rp, ci, va, B)
+    assert C16.dtype == torch.float32 and float((C - C16).norm() / C.norm()) < 5e-3
+    plan = ra_spmm.make_cusparse_plan(rp, ci, va, torch.empty_like(B))        # the callers pass a template operand
+    assert float((ra_spmm.run_cusparse_plan(plan, B) - C).norm() / C.norm()) < 1e-5
+
+
 def test_plan_checksums_are_reproducible_and_match_the_oracle(graph):
     a, rp, ci, va, B = graph
     p1 = ra_spmm.make_community_tc_plan(rp, ci, va, a.M, a.K, 64)
