@@ -600,6 +600,21 @@ def main():
     ms_e2e = timed_loop(torch, lambda: e2e_run(e2e_steps), 1, dist_on)[0] / e2e_steps
     e2e_gflops = 2.0 * nnz * N / (ms_e2e * 1e-3) / 1e9
     h2d_bytes = int(slab_host.numel() * slab_host.element_size()) * n_gpus
+
+    # ---- row-sharded B, device-resident: every rank holds only its K/P-row slab of B; a step is
+    # one NCCL all-gather of the slabs followed by the rank's SpMM (the exchange a caller pays when
+    # the dense operand is produced sharded, as between two GNN layers) ----
+    sharded_b = None
+    if dist_on:
+        def sharded_step():
+            dist.all_gather_into_tensor(B_stage[0], slab_dev[0])
+            runner(B_stage[0][:K])
+        for _ in range(3):
+            sharded_step()
+        ms_sh = timed_loop(torch, sharded_step, args.steps, dist_on)[0] / args.steps
+        sharded_b = {"ms_per_step": ms_sh, "value": 2.0 * nnz * N / (ms_sh * 1e-3) / 1e9, "unit": UNIT,
+                     "gathered_bytes_per_rank": int(slab_host.numel() * slab_host.element_size()) * (world - 1),
+                     "path": "K/P-row slab of B resident per rank -> NCCL all-gather -> SpMM on the rank's row block"}
     del B_stage, slab_dev
     torch.cuda.empty_cache()
 
@@ -649,6 +664,8 @@ def main():
             "gpu_launches": runner.launches * args.steps * n_gpus,
             "edgewise_gbs": (4 * (M + 1) + (4 + sA) * nnz + sB * nnz * N + 4 * M * N) / (ms_step * 1e-3) / 1e9,
         }
+        if sharded_b is not None:
+            line["sharded_b"] = sharded_b
         if n_gpus > 1:
             # balance report: per-rank step time and the nonzeros / rows of each row block
             line["ranks"] = {"ms_per_step": rank_ms_step,
