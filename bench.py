@@ -244,6 +244,8 @@ class Runner:
         self.tf32 = kernel.endswith("_TF32")
         self.plan = None
         self.launches = 1
+        torch.cuda.synchronize()
+        t_plan = time.perf_counter()
         if fam == "ZERO_OVERHEAD_CSR":
             self.plan = ra_spmm.make_zero_overhead_plan(self.rp, self.M, K)
             data = (self.plan.num_chunks > 0) + (self.plan.num_small > 0)
@@ -260,6 +262,10 @@ class Runner:
             self.launches = 1 + (self.plan.num_split_windows > 0)
         elif fam != "CSR_DIRECT":
             raise SystemExit(f"unknown kernel {kernel}")
+        torch.cuda.synchronize()
+        # wall-clock time of the plan build from device-resident CSR (for COMMUNITY_TC it includes
+        # the locality sort, for the tile families the window sort and the packing of the blocks)
+        self.plan_ms = (time.perf_counter() - t_plan) * 1e3
         if fam in ("TC_DIRECT", "COMMUNITY_TC", "SEGMENT_HYBRID") and not self.tf32 and b_dtype == "float32":
             self.launches += 1                     # per-call fp32 -> fp16 conversion of B
         self.fam = fam
@@ -442,7 +448,7 @@ def measure_entry(torch, dist, args, cfg, selector, dev, world, rank, peak):
              "ms_per_step": ms, "gflops": 2.0 * a.nnz * N / (ms * 1e-3) / 1e9,
              "bytes_algo": bytes_algo, "nnz": a.nnz, "N": N,
              "roofline_frac": bytes_algo / (ms * 1e-3) / 1e9 / (peak * world),
-             "warmup": args.inner_warmup, "iters": args.inner_iters}
+             "warmup": args.inner_warmup, "iters": args.inner_iters, "plan_build_ms": runner.plan_ms}
     tb, src = traffic_entry(cfg, kernel)
     if tb is not None and world == 1 and args.scale == 1.0:
         entry["traffic"], entry["traffic_source"] = tb, src
@@ -654,7 +660,8 @@ def main():
                                     f"then tuned from the measured time of each rank's block; B replicated, "
                                     f"no collective in the device-timed SpMM",
                        "l2": f"inputs larger than L2: B {sB * K * N / 1e6:.0f} MB + C {4 * M * N / 1e6:.0f} MB per step",
-                       "a_resident": "CSR arrays and the plan are uploaded/built once (warm protocol)"},
+                       "a_resident": "CSR arrays and the plan are uploaded/built once (warm protocol)",
+                       "plan_build_ms": runner.plan_ms},
             "roofline": roof, "clocks": clocks,
             "e2e": {"value": e2e_gflops, "unit": UNIT, "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": int(4 * M * N), "steps": e2e_steps,
@@ -699,22 +706,24 @@ def main():
             except Exception as exc:                # one entry failing must not lose the headline
                 also.append({"config": cfg, "selector": sel, "error": f"{type(exc).__name__}: {exc}"})
         # configuration 5: the 2-layer GCN training step on the row-partitioned operator
-        # (forward + backward + Adam; NCCL all-gather of each layer's row slabs at N > 1)
-        try:
-            from ra_spmm_b200 import gcn_bench
-            gargs = gcn_bench.parse_args(["--scale", str(args.scale), "--steps", "10", "--warmup", "3",
-                                          "--panels", str(args.gcn_panels if dist_on else 1)])
-            g = gcn_bench.measure(gargs, world, rank, dev)
-            if rank == 0:
-                also.append({"config": "C5", "kernel": "2-layer GCN step, routed SpMM (" +
-                             ", ".join(f"N={k}: {v}" for k, v in sorted(g["config"]["labels"].items())) + ")",
-                             "gcn_step_ms": g["value"], "spmm_gflops": g["spmm_gflops"], "loss": g["loss"],
-                             "steps": g["steps"], "warmup": g["warmup"], "workload": g["config"]["workload"],
-                             "allgather_bytes_per_step_per_rank": g["config"]["allgather_bytes_per_step_per_rank"],
-                             "panels": g["config"]["panels"]})
-        except Exception as exc:
-            if rank == 0:
-                also.append({"config": "C5", "error": f"{type(exc).__name__}: {exc}"})
+        # (forward + backward + Adam; NCCL all-gather of each layer's row slabs at N > 1),
+        # once with the routed kernels (FP16 tile path) and once all in fp32 through CSR_DIRECT
+        from ra_spmm_b200 import gcn_bench
+        for gk in ("routed", "CSR_DIRECT"):
+            try:
+                gargs = gcn_bench.parse_args(["--scale", str(args.scale), "--steps", "10", "--warmup", "3",
+                                              "--kernel", gk, "--panels", str(args.gcn_panels if dist_on else 1)])
+                g = gcn_bench.measure(gargs, world, rank, dev)
+                if rank == 0:
+                    also.append({"config": "C5", "kernel": f"2-layer GCN step, {gk} SpMM (" +
+                                 ", ".join(f"N={k}: {v}" for k, v in sorted(g["config"]["labels"].items())) + ")",
+                                 "gcn_step_ms": g["value"], "spmm_gflops": g["spmm_gflops"], "loss": g["loss"],
+                                 "steps": g["steps"], "warmup": g["warmup"], "workload": g["config"]["workload"],
+                                 "allgather_bytes_per_step_per_rank": g["config"]["allgather_bytes_per_step_per_rank"],
+                                 "panels": g["config"]["panels"]})
+            except Exception as exc:
+                if rank == 0:
+                    also.append({"config": "C5", "kernel": gk, "error": f"{type(exc).__name__}: {exc}"})
         if rank == 0:
             line["also"] = also
             line["gpu_launches"] += sum(e.get("iters", 0) for e in also) * n_gpus
