@@ -147,6 +147,36 @@ RA_API int ra_route_details(const RaFeatures* features, int portfolio, const RaR
                             RaRouteDetails* out);
 RA_API const char* ra_reject_reason_name(int code);   /* reject_reason_str, ra_common.h:162-179 */
 
+/* ---- structural analysis (the 34 features of the research portfolio) ------------------
+ * Replaces compute_router_features (router/router_features.cpp:113-432) as the binding
+ * analyze_matrix publishes it (bindings/ra_bindings.cpp:1993-2051): degree statistics, fill
+ * statistics of the nonempty 16x16 tiles, 64-bucket column signatures of the rows and the
+ * locality / partition proxies derived from them over 16-row windows. Field names, order and
+ * arithmetic are the reference's (RouterFeatures, ra_common.h:185-231); every field is
+ * bit-exact with it on duplicate-free CSR. The O(nnz) parts (tile counts by radix sort, per-row
+ * column sums and signatures, the proxy row order) run on the device and produce integers
+ * only; the order-sensitive floating-point reductions over rows and windows run on the host in
+ * the reference's order. rowptr/colind: host or device pointers (on_device). Blocks until the
+ * result is on the host. RA_ERR_UNSUPPORTED when a 16x16 tile holds more than 256 entries
+ * (duplicate (row, column) pairs). */
+typedef struct RaMatrixAnalysis {
+    float avg_nnz_per_row, std_nnz_per_row, degree_cv, max_to_mean_ratio, frac_dense_rows,
+          skew_ratio, long_row_fraction, long_row_nnz_fraction, top_1_row_nnz_fraction,
+          top_5_row_nnz_fraction;
+    float tile_fill_mean, tile_fill_median, tile_fill_p90, tile_fill_max, tile_fill_variance,
+          tile_occupancy, actual_nnz_coverage, avg_nnz_per_tile, row_window_colspan_compactness,
+          local_row_similarity_proxy, reordered_locality_proxy, locality_gain_proxy,
+          locality_selectivity_proxy, road_likeness_proxy, row_split_affinity_proxy,
+          mixedness_proxy;
+    float tc_candidate_ratio, tc_synergy_proxy, estimated_tc_partition_ratio,
+          estimated_cuda_partition_ratio, irregular_window_fraction, tc_granularity_proxy,
+          redundancy_risk_proxy;
+    int32_t tc_candidate_tiles;
+    int32_t output_dim_N, matrix_M, matrix_K, total_nnz;
+} RaMatrixAnalysis;
+RA_API int ra_analyze_matrix(const int32_t* rowptr, const int32_t* colind, int on_device,
+                             int M, int K, int N, void* stream, RaMatrixAnalysis* out);
+
 /* ---- CSR_DIRECT --------------------------------------------------------
  * Replaces csr_direct_spmm (csr/csr_direct.cu:234-338). C is fully overwritten
  * (empty rows become zero rows). */

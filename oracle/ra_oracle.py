@@ -466,3 +466,208 @@ def rel_fro(x, ref):
     den = np.linalg.norm(ref)
     num = np.linalg.norm(np.asarray(x, dtype=np.float64) - ref)
     return float(num / den) if den > 0 else float(num)
+
+
+# ---- structural analysis: the 34 features of the research portfolio --------------------
+_F = np.float32
+
+
+def _clamp01(x):
+    return _F(max(_F(0), min(_F(1), _F(x))))
+
+
+def _sdiv(num, den):
+    num, den = _F(num), _F(den)
+    return _F(num / den) if abs(den) > _F(1e-6) else _F(0)
+
+
+def _popcount(x: int) -> int:
+    return bin(int(x)).count("1")
+
+
+def _jaccard(a: int, b: int):
+    uni = _popcount(a | b)
+    return _F(0) if uni == 0 else _F(_F(_popcount(a & b)) / _F(uni))
+
+
+def _mean_f(values):
+    """float(sum in double, in order, / count): safe_mean, router/router_features.cpp:62-72."""
+    if len(values) == 0:
+        return _F(0)
+    s = 0.0
+    for v in values:
+        s += float(v)
+    return _F(s / float(len(values)))
+
+
+def analyze_matrix(rowptr, colind, M, K, N):
+    """compute_router_features (router/router_features.cpp:113-432) restated with the same
+    arithmetic types and the same order of the floating-point additions. Python loops over rows,
+    tiles and windows: for small matrices. Returns {field name: np.float32 | int}."""
+    rowptr = np.asarray(rowptr, dtype=np.int64)
+    colind = np.asarray(colind, dtype=np.int64)
+    keys_f = ("avg_nnz_per_row", "std_nnz_per_row", "degree_cv", "max_to_mean_ratio", "frac_dense_rows", "skew_ratio",
+              "long_row_fraction", "long_row_nnz_fraction", "top_1_row_nnz_fraction", "top_5_row_nnz_fraction",
+              "tile_fill_mean", "tile_fill_median", "tile_fill_p90", "tile_fill_max", "tile_fill_variance",
+              "tile_occupancy", "actual_nnz_coverage", "avg_nnz_per_tile", "row_window_colspan_compactness",
+              "local_row_similarity_proxy", "reordered_locality_proxy", "locality_gain_proxy",
+              "locality_selectivity_proxy", "road_likeness_proxy", "row_split_affinity_proxy", "mixedness_proxy",
+              "tc_candidate_ratio", "tc_synergy_proxy", "estimated_tc_partition_ratio", "estimated_cuda_partition_ratio",
+              "irregular_window_fraction", "tc_granularity_proxy", "redundancy_risk_proxy")
+    f = {k: _F(0) for k in keys_f}
+    f.update(tc_candidate_tiles=0, output_dim_N=0, matrix_M=0, matrix_K=0, total_nnz=0)
+    if M <= 0 or K <= 0:
+        return f
+    nnz = int(rowptr[M])
+    f.update(matrix_M=int(M), matrix_K=int(K), output_dim_N=int(N), total_nnz=nnz)
+    if nnz <= 0:
+        return f
+
+    lens = np.diff(rowptr[:M + 1]).astype(np.int64)
+    first = np.zeros(M, dtype=np.int64); last = np.zeros(M, dtype=np.int64)
+    sig = [0] * M
+    centroid = np.zeros(M, dtype=np.float32)
+    for r in range(M):
+        b, e = int(rowptr[r]), int(rowptr[r + 1])
+        if e > b:
+            cols = colind[b:e]
+            first[r], last[r] = cols[0], cols[-1]
+            s = 0
+            for bucket in np.minimum(63, (cols * 64) // max(1, K)):
+                s |= 1 << int(bucket)
+            sig[r] = s
+            centroid[r] = _F(float(int(cols.sum())) / float(e - b))
+
+    # degree statistics
+    sum_lens = 0.0
+    for L in lens:
+        sum_lens += float(L)
+    avg = sum_lens / float(M)
+    var = 0.0
+    dense_rows = long_rows = long_row_nnz = 0
+    thr = max(32.0, 2.0 * avg)
+    for L in lens:
+        d = float(L) - avg
+        var += d * d
+        if float(L) > 2.0 * avg:
+            dense_rows += 1
+        if float(L) >= thr:
+            long_rows += 1; long_row_nnz += int(L)
+    std = float(np.sqrt(np.float64(var / float(max(1, M)))))
+    top = np.sort(lens)[::-1]
+    max_len = int(top[0])
+    f["avg_nnz_per_row"] = _F(avg)
+    f["std_nnz_per_row"] = _F(std)
+    f["degree_cv"] = _F(std / avg) if avg > 1e-6 else _F(0)
+    f["max_to_mean_ratio"] = _F(float(max_len) / avg) if avg > 1e-6 else _F(0)
+    f["frac_dense_rows"] = _F(_F(dense_rows) / _F(max(1, M)))
+    f["skew_ratio"] = f["max_to_mean_ratio"]
+    f["long_row_fraction"] = _F(_F(long_rows) / _F(max(1, M)))
+    f["long_row_nnz_fraction"] = _F(_F(long_row_nnz) / _F(max(1, nnz)))
+    f["top_1_row_nnz_fraction"] = _F(_F(int(top[0])) / _F(max(1, nnz)))
+    f["top_5_row_nnz_fraction"] = _F(_F(int(top[:5].sum())) / _F(max(1, nnz)))
+
+    # 16x16 tiles
+    tile_rows, tile_cols = (M + 15) // 16, (K + 15) // 16
+    rows_of = np.repeat(np.arange(M, dtype=np.int64), lens)
+    tkeys = (rows_of // 16) * tile_cols + colind[:nnz] // 16
+    _, counts = np.unique(tkeys, return_counts=True)
+    fills = np.sort((counts.astype(np.float32) / _F(256)).astype(np.float32))
+    nt = fills.size
+    fill_mean = _mean_f(fills)
+    fv = 0.0
+    for x in fills:
+        d = float(x) - float(fill_mean)
+        fv += d * d
+    fv = fv / float(nt) if nt else 0.0
+    cand = fills >= _F(0.25)
+    f["tile_fill_mean"] = fill_mean
+    f["tile_fill_median"] = fills[nt // 2] if nt else _F(0)
+    f["tile_fill_p90"] = fills[min(nt - 1, (nt * 9) // 10)] if nt else _F(0)
+    f["tile_fill_max"] = fills[-1] if nt else _F(0)
+    f["tile_fill_variance"] = _F(fv)
+    f["tile_occupancy"] = _F(_F(nt) / _F(max(1, tile_rows * tile_cols)))
+    f["actual_nnz_coverage"] = _F(_F(int(counts[counts >= 64].sum())) / _F(max(1, nnz)))
+    f["avg_nnz_per_tile"] = _F(_F(nnz) / _F(nt)) if nt else _F(0)
+    f["tc_candidate_tiles"] = int(cand.sum())
+    f["tc_candidate_ratio"] = _F(_F(f["tc_candidate_tiles"]) / _F(nt)) if nt else _F(0)
+
+    # similarity of neighbouring rows, stored order and proxy order
+    f["local_row_similarity_proxy"] = _mean_f([_jaccard(sig[r - 1], sig[r]) for r in range(1, M)
+                                                if lens[r - 1] > 0 and lens[r] > 0])
+    bucket = np.array([int(_F(_F(centroid[r] * _F(16)) / _F(K))) for r in range(M)], dtype=np.int64)
+    span = np.where(lens > 0, last - first + 1, K)
+    order = sorted(range(M), key=lambda r: (bucket[r], span[r], -lens[r]))        # sorted() is stable
+    f["reordered_locality_proxy"] = _mean_f([_jaccard(sig[a], sig[b]) for a, b in zip(order[:-1], order[1:])
+                                              if lens[a] > 0 and lens[b] > 0])
+
+    # 16-row windows
+    comp_l, sim_l, irr_l = [], [], []
+    tc_nnz = cuda_nnz = irregular = 0
+    for base in range(0, M, 16):
+        end = min(M, base + 16)
+        wn = int(lens[base:end].sum()); max_row = int(lens[base:end].max())
+        mn, mx = K, -1
+        sim_sum, sim_cnt = _F(0), 0
+        for r in range(base, end):
+            if lens[r] > 0:
+                mn, mx = min(mn, int(first[r])), max(mx, int(last[r]))
+            if r > base and lens[r - 1] > 0 and lens[r] > 0:
+                sim_sum = _F(sim_sum + _jaccard(sig[r - 1], sig[r])); sim_cnt += 1
+        avg_row = _F(_F(wn) / _F(max(1, end - base)))
+        wthr = max(_F(32), _F(_F(2.5) * avg_row))
+        long_nnz = int(sum(int(lens[r]) for r in range(base, end) if _F(int(lens[r])) >= wthr))
+        sp = (mx - mn + 1) if mx >= mn else K
+        compact = _F(_F(wn) / _F(max(1, (end - base) * max(1, sp))))
+        sim = _F(sim_sum / _F(sim_cnt)) if sim_cnt > 0 else _F(0)
+        aligned = max(16, ((sp + 15) // 16) * 16)
+        dens = _F(_F(wn) / _F(max(16, (end - base) * aligned)))
+        cn = _clamp01(_F(compact * _F(6)))
+        dn = _clamp01(_F(dens * _F(10)))
+        un = _clamp01(_F(_F(1) - _sdiv(_F(max_row), _F(_F(_F(4) * avg_row) + _F(1)))))
+        lm = _sdiv(_F(long_nnz), _F(max(1, wn)))
+        comp_l.append(compact); sim_l.append(sim)
+        tc_score = _F(_F(_F(_F(_F(0.35) * cn) + _F(_F(0.30) * sim)) + _F(_F(0.20) * dn)) + _F(_F(0.15) * un))
+        irr = _F(_F(_F(_F(_F(0.40) * lm) +
+                       _F(_F(0.25) * _clamp01(_F(_sdiv(_F(max_row), _F(avg_row + _F(1))) / _F(6))))) +
+                    _F(_F(0.20) * _F(_F(1) - cn))) + _F(_F(0.15) * _F(_F(1) - sim)))
+        irr_l.append(irr)
+        if avg_row >= _F(8) and tc_score >= _F(0.55) and irr < _F(0.45):
+            tc_nnz += wn
+        if irr >= _F(0.50) or lm >= _F(0.20):
+            cuda_nnz += wn; irregular += 1
+
+    g = f
+    g["row_window_colspan_compactness"] = _mean_f(comp_l)
+    wsim, wirr = _mean_f(sim_l), _mean_f(irr_l)
+    g["tc_synergy_proxy"] = _F(_F(_F(_F(_F(0.35) * _clamp01(_F(g["tile_fill_mean"] / _F(0.20)))) +
+                                      _F(_F(0.25) * g["tc_candidate_ratio"])) +
+                                   _F(_F(0.20) * g["reordered_locality_proxy"])) +
+                               _F(_F(0.20) * g["row_window_colspan_compactness"]))
+    g["locality_gain_proxy"] = _clamp01(_F(g["reordered_locality_proxy"] - g["local_row_similarity_proxy"]))
+    ordered = _clamp01(_F(g["local_row_similarity_proxy"] * _clamp01(_F(g["row_window_colspan_compactness"] * _F(2)))))
+    g["locality_selectivity_proxy"] = _clamp01(_F(g["locality_gain_proxy"] * _F(_F(1) - ordered)))
+    g["road_likeness_proxy"] = _clamp01(_F(_F(_F(g["local_row_similarity_proxy"] *
+                                                  _clamp01(_F(_F(1) - _F(g["degree_cv"] / _F(0.35))))) *
+                                               _clamp01(_F(_F(1) - _F(g["avg_nnz_per_row"] / _F(24))))) *
+                                            _clamp01(_F(g["row_window_colspan_compactness"] / _F(0.25)))))
+    skew = _F(_F(_F(_F(_F(0.45) * _clamp01(_F(_F(g["skew_ratio"] - _F(2.0)) / _F(6.0)))) +
+                    _F(_F(0.30) * g["long_row_nnz_fraction"])) +
+                 _F(_F(0.15) * _clamp01(_F(g["top_1_row_nnz_fraction"] / _F(0.0020))))) +
+              _F(_F(0.10) * _clamp01(_F(g["top_5_row_nnz_fraction"] / _F(0.0100)))))
+    n_scale = _clamp01(_F(_F(_F(N) - _F(128)) / _F(384)))
+    dense_reg = _F(_clamp01(_F(g["avg_nnz_per_row"] / _F(192))) * _F(_F(0.35) + _F(_F(0.65) * n_scale)))
+    g["row_split_affinity_proxy"] = _clamp01(max(skew, dense_reg))
+    g["estimated_tc_partition_ratio"] = _clamp01(_F(_F(tc_nnz) / _F(max(1, nnz))))
+    g["estimated_cuda_partition_ratio"] = _clamp01(_F(_F(cuda_nnz) / _F(max(1, nnz))))
+    g["irregular_window_fraction"] = _F(_F(irregular) / _F(max(1, (M + 15) // 16)))
+    tcr, cur = g["estimated_tc_partition_ratio"], g["estimated_cuda_partition_ratio"]
+    balance = _sdiv(_F(_F(2) * min(tcr, cur)), _F(_F(tcr + cur) + _F(1e-6)))
+    g["mixedness_proxy"] = _clamp01(_F(balance * _clamp01(_F(_F(tcr + cur) / _F(0.60)))))
+    g["tc_granularity_proxy"] = _F(_F(_F(0.55) * _clamp01(_F(g["avg_nnz_per_row"] / _F(64)))) +
+                                   _F(_F(0.45) * _clamp01(_F(_F(_F(1) - g["long_row_fraction"]) +
+                                                              _F(_F(0.5) * g["locality_selectivity_proxy"])))))
+    g["redundancy_risk_proxy"] = _clamp01(_F(_F(_F(_F(_F(0.45) * g["long_row_nnz_fraction"]) +
+                                                   _F(_F(0.30) * _F(_F(1) - g["row_window_colspan_compactness"]))) +
+                                                _F(_F(0.15) * _F(_F(1) - wsim))) + _F(_F(0.10) * wirr)))
+    return f

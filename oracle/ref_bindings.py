@@ -70,8 +70,35 @@ def router():
         if hasattr(lib, "ref_route_details_from_features"):
             lib.ref_route_details_from_features.argtypes = [C.c_float, C.c_float, C.c_float, C.c_int, C.c_int,
                                                             C.c_int, C.c_int, C.POINTER(RefRouteDetails)]
+        if hasattr(lib, "ref_analyze_matrix"):
+            lib.ref_analyze_matrix.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
         lib._typed = True
     return lib
+
+
+ANALYSIS_FLOAT_KEYS = (
+    "avg_nnz_per_row", "std_nnz_per_row", "degree_cv", "max_to_mean_ratio", "frac_dense_rows", "skew_ratio",
+    "long_row_fraction", "long_row_nnz_fraction", "top_1_row_nnz_fraction", "top_5_row_nnz_fraction",
+    "tile_fill_mean", "tile_fill_median", "tile_fill_p90", "tile_fill_max", "tile_fill_variance",
+    "tile_occupancy", "actual_nnz_coverage", "avg_nnz_per_tile", "row_window_colspan_compactness",
+    "local_row_similarity_proxy", "reordered_locality_proxy", "locality_gain_proxy",
+    "locality_selectivity_proxy", "road_likeness_proxy", "row_split_affinity_proxy", "mixedness_proxy",
+    "tc_candidate_ratio", "tc_synergy_proxy", "estimated_tc_partition_ratio", "estimated_cuda_partition_ratio",
+    "irregular_window_fraction", "tc_granularity_proxy", "redundancy_risk_proxy")
+ANALYSIS_INT_KEYS = ("tc_candidate_tiles", "output_dim_N", "matrix_M", "matrix_K", "total_nnz")
+
+
+def ref_analyze_matrix(rowptr, colind, M, K, N) -> dict:
+    """compute_router_features of the reference (router/router_features.cpp:113-432): the 33
+    float fields as np.float32 and the five int fields, keyed by field name."""
+    rp = np.ascontiguousarray(rowptr, dtype=np.int32)
+    ci = np.ascontiguousarray(colind, dtype=np.int32)
+    f = np.zeros(33, dtype=np.float32)
+    i = np.zeros(5, dtype=np.int32)
+    router().ref_analyze_matrix(rp.ctypes.data, ci.ctypes.data, M, K, N, f.ctypes.data, i.ctypes.data)
+    out = {k: f[j] for j, k in enumerate(ANALYSIS_FLOAT_KEYS)}
+    out.update({k: int(i[j]) for j, k in enumerate(ANALYSIS_INT_KEYS)})
+    return out
 
 
 def ref_route_details_from_features(avg, std, cv, M, K, N, nnz) -> RefRouteDetails:

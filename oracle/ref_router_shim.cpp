@@ -2,7 +2,8 @@
 // reference sources where they lie (see Makefile). TEST INFRASTRUCTURE ONLY.
 // Wraps compute_production_router_features (router/router_features.cpp:79-111),
 // compute_router_scores (router/router_scores.cpp) and route_dispatch
-// (router/router_dispatch.cpp:649-1113).
+// (router/router_dispatch.cpp:649-1113), and compute_router_features
+// (router/router_features.cpp:113-432).
 #include "router/router.h"
 
 #include <cstring>
@@ -76,6 +77,16 @@ int ref_route_details_from_features(float avg, float stddev, float cv, int M, in
     }
     out->gate_margin_raw = plan.gate_margin_raw;
     out->gate_margin_norm = plan.gate_margin_norm;
+    return 0;
+}
+
+// the 34 structural features: the leading 33 floats of RouterFeatures in declaration order,
+// then tc_candidate_tiles, output_dim_N, matrix_M, matrix_K, total_nnz
+int ref_analyze_matrix(const int* rowptr, const int* colind, int M, int K, int N, float* out33, int* out5) {
+    const RouterFeatures f = compute_router_features(rowptr, colind, M, K, N);
+    std::memcpy(out33, &f.avg_nnz_per_row, 33 * sizeof(float));
+    out5[0] = f.tc_candidate_tiles; out5[1] = f.output_dim_N; out5[2] = f.matrix_M;
+    out5[3] = f.matrix_K; out5[4] = f.total_nnz;
     return 0;
 }
 

@@ -27,7 +27,7 @@ DTYPE_F32, DTYPE_F16 = 0, 1
 EXPORTED_SYMBOLS = [
     "ra_last_error_string", "ra_path_name", "ra_version", "ra_copy_to_host", "ra_fnv1a64_host",
     "ra_features_from_rowptr_host", "ra_features_from_rowptr_device", "ra_route",
-    "ra_route_details", "ra_reject_reason_name",
+    "ra_route_details", "ra_reject_reason_name", "ra_analyze_matrix",
     "ra_csr_direct_spmm",
     "ra_zo_plan_create", "ra_zo_plan_info", "ra_zo_plan_run", "ra_zo_plan_destroy",
     "ra_zo_plan_run_phases", "ra_zo_plan_run_noalloc",
@@ -62,6 +62,22 @@ class RaRouteDetails(C.Structure):
         ("rejection_detail", (C.c_char * 128) * PATH_COUNT),
         ("gate_margin_raw", C.c_float), ("gate_margin_norm", C.c_float),
     ]
+
+
+ANALYSIS_FLOAT_KEYS = (
+    "avg_nnz_per_row", "std_nnz_per_row", "degree_cv", "max_to_mean_ratio", "frac_dense_rows", "skew_ratio",
+    "long_row_fraction", "long_row_nnz_fraction", "top_1_row_nnz_fraction", "top_5_row_nnz_fraction",
+    "tile_fill_mean", "tile_fill_median", "tile_fill_p90", "tile_fill_max", "tile_fill_variance",
+    "tile_occupancy", "actual_nnz_coverage", "avg_nnz_per_tile", "row_window_colspan_compactness",
+    "local_row_similarity_proxy", "reordered_locality_proxy", "locality_gain_proxy",
+    "locality_selectivity_proxy", "road_likeness_proxy", "row_split_affinity_proxy", "mixedness_proxy",
+    "tc_candidate_ratio", "tc_synergy_proxy", "estimated_tc_partition_ratio", "estimated_cuda_partition_ratio",
+    "irregular_window_fraction", "tc_granularity_proxy", "redundancy_risk_proxy")
+ANALYSIS_INT_KEYS = ("tc_candidate_tiles", "output_dim_N", "matrix_M", "matrix_K", "total_nnz")
+
+
+class RaMatrixAnalysis(C.Structure):
+    _fields_ = [(k, C.c_float) for k in ANALYSIS_FLOAT_KEYS] + [(k, C.c_int32) for k in ANALYSIS_INT_KEYS]
 
 
 class RaZoInfo(C.Structure):
@@ -125,6 +141,7 @@ def load() -> C.CDLL:
     lib.ra_route.argtypes = [C.POINTER(RaFeatures), i32, C.POINTER(RaRoute)]
     lib.ra_route_details.argtypes = [C.POINTER(RaFeatures), i32, C.POINTER(RaRoute), C.POINTER(RaRouteDetails)]
     lib.ra_reject_reason_name.argtypes = [i32]
+    lib.ra_analyze_matrix.argtypes = [vp, vp, i32, i32, i32, i32, vp, C.POINTER(RaMatrixAnalysis)]
     lib.ra_reject_reason_name.restype = C.c_char_p
     lib.ra_csr_direct_spmm.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i64, vp]
     lib.ra_zo_plan_create.argtypes = [vp, i32, i32, i32, vp, C.POINTER(vp)]

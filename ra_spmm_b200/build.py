@@ -69,7 +69,10 @@ def build(verbose: bool = False, ptxas_info: bool = False) -> Path:
         with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
             list(ex.map(run, jobs))
     if jobs or _stale(LIB_PATH, objs):
-        run([NVCC, "-shared", "-o", str(LIB_PATH), *map(str, objs), "-lcudart"])
+        # link beside the target and rename: a reader never sees a half-written library
+        tmp = LIB_PATH.with_suffix(".so.tmp")
+        run([NVCC, "-shared", "-o", str(tmp), *map(str, objs), "-lcudart"])
+        os.replace(tmp, LIB_PATH)
     return LIB_PATH
 
 

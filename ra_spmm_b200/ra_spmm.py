@@ -32,7 +32,7 @@ __all__ = [
     "make_tc_direct_plan", "make_tc_direct_zc_plan", "run_tc_direct_plan", "run_tc_direct_plan_tf32",
     "make_community_tc_plan", "run_community_tc_plan", "run_community_tc_plan_tf32",
     "make_segment_hybrid_plan", "run_segment_hybrid_plan", "run_segment_hybrid_plan_tf32",
-    "make_router_plan", "run_router_plan", "gpu_info_next",
+    "make_router_plan", "run_router_plan", "gpu_info_next", "analyze_matrix",
     "spmm_cusparse", "spmm_cusparse_fp16", "make_cusparse_plan", "run_cusparse_plan",
     "benchmark_cusparse", "benchmark_cusparse_cold", "benchmark_cusparse_fp16", "benchmark_cusparse_fp16_cold",
     "RAZeroOverheadPlan", "RATcDirectPlan", "RACommunityTCPlan", "RASegmentHybridPlan",
@@ -639,6 +639,26 @@ def run_router_plan(plan_dict, rowptr, colind, vals, B):
         raise RaSpmmError(f"run_router_plan: path {path} is not part of this library")
     torch.cuda.synchronize(B.device)
     return out
+
+
+def analyze_matrix(rowptr, colind, M, K, N=128):
+    """The 34 structural features as a dict with the keys of the reference's analyze_matrix
+    (bindings/ra_bindings.cpp:1993-2051), plus "nnz". rowptr/colind: int32 tensors, both on the
+    CPU or both on the current CUDA device; the O(nnz) work runs on the GPU either way."""
+    if rowptr.is_cuda != colind.is_cuda:
+        raise RuntimeError("rowptr and colind must be on the same device")
+    rp = rowptr.contiguous().to(torch.int32)
+    ci = colind.contiguous().to(torch.int32)
+    out = _capi.RaMatrixAnalysis()
+    dev = rp.device if rp.is_cuda else torch.device("cuda", torch.cuda.current_device())
+    with torch.cuda.device(dev):
+        st = _lib().ra_analyze_matrix(rp.data_ptr(), ci.data_ptr(), 1 if rp.is_cuda else 0, int(M), int(K), int(N),
+                                      _stream_ptr(dev), C.byref(out))
+    _capi.check(st, "analyze_matrix")
+    d = {k: float(getattr(out, k)) for k in _capi.ANALYSIS_FLOAT_KEYS}
+    d["tc_candidate_tiles"] = int(out.tc_candidate_tiles)
+    d["nnz"] = int(rp[M].item()) if M > 0 else 0
+    return d
 
 
 def gpu_info_next():
