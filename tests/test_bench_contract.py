@@ -27,3 +27,33 @@ def test_reference_arm_prints_one_contract_line():
     e2e = line["e2e"]
     assert e2e["value"] == line["value"] and e2e["h2d_bytes_per_step"] == 0 and e2e["d2h_bytes_per_step"] == 0
     assert line["vs_baseline"] is None
+
+
+import pytest  # noqa: E402
+
+
+@pytest.mark.gpu
+def test_gpu_arm_prints_one_contract_line_at_test_size():
+    """The GPU arm end to end at 2^-7 of configuration 4: one JSON line with the roofline, CPU
+    baseline, end-to-end, clock, launch-count and parity keys, and a parity verdict that holds."""
+    r = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--scale", str(2 ** -7), "--steps", "5", "--warmup", "3",
+                        "--also", "off", "--inner-warmup", "3", "--inner-iters", "5"],
+                       capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = [l for l in r.stdout.splitlines() if l.strip()]
+    assert len(lines) == 1, r.stdout
+    line = json.loads(lines[0])
+    assert "impl" not in line or line["impl"] != "reference"
+    assert line["metric"] == "spmm_gflops_warm" and line["n_gpus"] == 1 and line["steps"] == 5 and line["warmup"] >= 3
+    assert line["config"]["workload"].startswith("C4") and line["config"]["kernel"] == "SEGMENT_HYBRID_TF32"
+    assert line["config"]["routed_kernel"] and line["config"]["plan_build_ms"] > 0
+    roof = line["roofline"]
+    assert roof["bound"] == "hbm" and roof["peak"] > 0 and 0 < roof["frac"] < 1.5
+    assert abs(roof["achieved"] - roof["bytes_algo_per_step"] / (line["ms_per_step"] * 1e-3) / 1e9) < 1e-6 * roof["achieved"]
+    e2e = line["e2e"]
+    assert e2e["h2d_bytes_per_step"] == 4 * line["config"]["K"] * line["config"]["N"]
+    assert e2e["d2h_bytes_per_step"] == 4 * line["config"]["M"] * line["config"]["N"]
+    assert 0 < e2e["value"] < line["value"]
+    assert line["gpu_launches"] >= 5 and "reasons" in line["clocks"]
+    assert line["cpu_baseline"]["kind"] == "reference" and line["cpu_baseline"]["value"] > 0
+    assert line["parity"]["ok"] and line["parity"]["rel_fro_vs_cpu_sparse_mm"] < line["parity"]["tolerance"]
