@@ -163,6 +163,7 @@ class RowSharding:
         self.rank, self.world, self.group = rank, world, group
         self.max_rows = max((self.bounds[i + 1] - self.bounds[i] for i in range(world)), default=0)
         self.comm_bytes = 0
+        self._slabs = {}
 
     @property
     def rows(self):
@@ -181,18 +182,34 @@ class RowSharding:
         owner = np.searchsorted(b, colind, side="right") - 1
         return (owner * self.max_rows + (colind - b[owner])).astype(np.int32)
 
-    def all_gather_rows(self, local: torch.Tensor, async_op: bool = False):
-        """Gathered operand; with async_op the pair (operand, work handle to wait on)."""
+    def _padded_slab(self, local: torch.Tensor, dtype, width: int, keep: bool = True) -> torch.Tensor:
+        """This rank's slab in the gather layout: max_rows x width in `dtype`, filled from `local`
+        in one pass (conversion, column padding and row padding together). The buffer is kept per
+        (dtype, width) and its padding stays zero: only the live rectangle is rewritten. keep=False
+        (a gather that stays in flight while the next slab is prepared) takes a fresh buffer."""
+        key = (dtype, width, local.device)
+        buf = self._slabs.get(key) if keep else None
+        if buf is None:
+            buf = torch.zeros((self.max_rows, width), dtype=dtype, device=local.device)
+            if keep:
+                self._slabs[key] = buf
+        buf[: local.shape[0], : local.shape[1]].copy_(local)
+        return buf
+
+    def all_gather_rows(self, local: torch.Tensor, async_op: bool = False, dtype=None, width=None):
+        """Gathered operand; with async_op the pair (operand, work handle to wait on). dtype / width:
+        format of the gathered operand (default: that of `local`)."""
+        dtype = dtype or local.dtype
+        width = width or local.shape[1]
         if self.world == 1:
-            return (local, _Done()) if async_op else local
-        n = local.shape[1]
-        full = torch.empty((self.world * self.max_rows, n), dtype=local.dtype, device=local.device)
+            out = local if (dtype == local.dtype and width == local.shape[1]) else self._padded_slab(local, dtype, width)
+            return (out, _Done()) if async_op else out
+        full = torch.empty((self.world * self.max_rows, width), dtype=dtype, device=local.device)
         r0, r1 = self.rows
-        if r1 - r0 == self.max_rows:
-            src = local.contiguous()
-        else:                                   # pad this rank's slab to the common height
-            src = torch.zeros((self.max_rows, n), dtype=local.dtype, device=local.device)
-            src[: r1 - r0].copy_(local)
+        if r1 - r0 == self.max_rows and dtype == local.dtype and width == local.shape[1] and local.is_contiguous():
+            src = local
+        else:
+            src = self._padded_slab(local, dtype, width, keep=not async_op)
         work = dist.all_gather_into_tensor(full, src, group=self.group, async_op=async_op)
         self.comm_bytes += full.numel() * full.element_size()
         return (full, work) if async_op else full
@@ -225,12 +242,7 @@ def _gather_and_multiply(local, spmm: Callable, sharding: RowSharding, fmt, pane
     if sharding.world > 1 and fmt is not None:
         dtype, width = fmt(n)
         if dtype != local.dtype or width != n:
-            src = local.new_zeros((local.shape[0], width), dtype=dtype) if width != n else None
-            if src is None:
-                src = local.to(dtype)
-            else:
-                src[:, :n].copy_(local)
-            out = spmm(sharding.all_gather_rows(src))
+            out = spmm(sharding.all_gather_rows(local, dtype=dtype, width=width))
             return out[:, :n].contiguous() if width != n else out
     return spmm(sharding.all_gather_rows(local))
 
