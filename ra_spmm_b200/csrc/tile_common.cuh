@@ -29,6 +29,7 @@ struct TileArgs {
     int max_unit_blocks;       // blocks of the longest unit (window, or 64 for segments)
     float* C;
     float* scratch;
+    long long scratch_floats;     // capacity of scratch
 };
 
 __device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gsrc) {
@@ -142,5 +143,7 @@ __device__ __forceinline__ void bulk_copy_g2s(unsigned dst, const void* src, uns
 // TMA gather ring (tile_gather4.cu). RA_ERR_UNSUPPORTED = shape not covered, use another kernel.
 template <bool kTF32, int kMode>
 int launch_tile_gather4(const TileArgs& a, const void* B, long long K, cudaStream_t st, int* status);
+// floats of scratch that lets the ring share windows between groups (0: not applicable)
+long long tile_gather4_split_scratch_floats(bool tf32, int mode, const TileArgs& a);
 
 }  // namespace ra

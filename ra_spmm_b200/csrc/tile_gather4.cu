@@ -24,6 +24,16 @@
 //
 // Every wait is bounded: a warp whose stage never fills records the status word, collects
 // (under the same bound) the copies it still has in flight, and returns.
+//
+// Work division. The units (windows, or segments of SEGMENT_HYBRID) lie on one axis where unit u
+// with nb blocks occupies nb + 1 positions (its blocks, then its flush). Segments are at most 64
+// blocks, so a group takes a run of whole segments. Windows can be thousands of blocks long (one
+// window of 8 hub rows, or simply 490-block windows when a rank's share is two windows per
+// group), so for the window families the axis is cut into equal pieces wherever the cut falls:
+// a group may start and end inside a window. The part of a window that a group does not own
+// completely goes to a partial tile in scratch (two slots per group: the window it entered
+// through, the window it left through), and g4_chain_merge_kernel adds the partial tiles of a
+// window in block order - always the same order, so the result is reproducible - and writes its rows.
 #include "tile_common.cuh"
 
 #include <cuda.h>
@@ -75,12 +85,30 @@ __device__ __forceinline__ int4 ld_stream_first_int4(const int4* p) {      // re
 // shared-memory row of tensor-core k index j (see the header comment)
 __device__ __forceinline__ int g4_row_of_k(int j) { return (j < 4) ? 2 * j : 2 * (j - 4) + 1; }
 
+// Cut `w` of the work axis -> (unit U, absolute block Bk): everything before block Bk of unit U
+// lies before the cut. A cut that falls on a unit's flush position moves to the start of the next
+// unit, so Bk < unit_begin(U + 1) whenever Bk > unit_begin(U).
+template <int kMode>
+__device__ __forceinline__ void g4_cut(const TileArgs& a, long long w, int& U, long long& Bk) {
+    const long long total_w = a.total_blocks + a.num_units;
+    if (w >= total_w) { U = a.num_units; Bk = a.total_blocks; return; }
+    int u = unit_lower_bound<kMode>(a, w);                       // smallest u with begin(u) + u >= w
+    long long ub = unit_begin<kMode>(a, u);
+    if (u < a.num_units && ub + u == w) { U = u; Bk = ub; return; }
+    --u;                                                         // the cut is inside unit u
+    const long long ub0 = unit_begin<kMode>(a, u);
+    const long long off = w - (ub0 + u);                         // 1 .. nb(u)
+    if (ub0 + off >= ub) { U = u + 1; Bk = ub; } else { U = u; Bk = ub0 + off; }
+}
+
 // kMode: 0 natural windows, 1 window-row table (COMMUNITY_TC), 2 segments (SEGMENT_HYBRID).
+// split (modes 0 and 1): groups own equal pieces of the work axis and may share a window.
 // S: 128-byte slices per warp. D: ring stages per warp.
 template <bool kTF32, int kMode, int S, int D>
 __global__ void __launch_bounds__(256)
 tile_spmm_gather4_kernel(const __grid_constant__ CUtensorMap bmap, TileArgs a, int slices_total,
-                         int warps_per_group, int groups_total, int* __restrict__ status, unsigned wait_hint_ns, int l2_policies)
+                         int warps_per_group, int groups_total, int* __restrict__ status, unsigned wait_hint_ns, int l2_policies,
+                         int split)
 {
     constexpr int kMT    = kTF32 ? 2 : 4;           // 16-feature MMA tiles per slice
     constexpr int kElem  = kTF32 ? 4 : 2;
@@ -114,13 +142,26 @@ tile_spmm_gather4_kernel(const __grid_constant__ CUtensorMap bmap, TileArgs a, i
     __syncwarp();
     if (!has_work) return;
 
-    // ---- this group's contiguous unit range, balanced by blocks + units ----
+    // ---- this group's piece of the work axis (blocks + one flush position per unit) ----
     const long long total_w = a.total_blocks + a.num_units;
-    const int u_lo = unit_lower_bound<kMode>(a, total_w * gid / groups_total);
-    const int u_hi = unit_lower_bound<kMode>(a, total_w * (gid + 1) / groups_total);
+    int u_lo, u_hi;                                              // units [u_lo, u_hi) are touched
+    long long B0, B1;                                            // absolute block range
+    bool head_partial = false, tail_partial = false;            // first / last touched unit shared with a neighbour
+    if (kMode != 2 && split) {
+        int us, ue; long long bs, be;
+        g4_cut<kMode>(a, total_w * gid / groups_total, us, bs);
+        g4_cut<kMode>(a, total_w * (gid + 1) / groups_total, ue, be);
+        tail_partial = ue < a.num_units && be > unit_begin<kMode>(a, ue);
+        head_partial = us < a.num_units && bs > unit_begin<kMode>(a, us);
+        u_lo = us; u_hi = tail_partial ? ue + 1 : ue;
+        B0 = bs; B1 = be;
+    } else {
+        u_lo = unit_lower_bound<kMode>(a, total_w * gid / groups_total);
+        u_hi = unit_lower_bound<kMode>(a, total_w * (gid + 1) / groups_total);
+        B0 = unit_begin<kMode>(a, u_lo); B1 = unit_begin<kMode>(a, u_hi);
+    }
     if (u_lo >= u_hi) return;
-    const long long B0 = unit_begin<kMode>(a, u_lo);
-    const int nb = (int)(unit_begin<kMode>(a, u_hi) - B0);      // blocks of this range
+    const int nb = (int)(B1 - B0);                               // blocks of this piece
 
     const int N = a.N;
     const int slice0 = part * S;                                 // first slice of this warp
@@ -184,14 +225,21 @@ tile_spmm_gather4_kernel(const __grid_constant__ CUtensorMap bmap, TileArgs a, i
 
 #pragma unroll 1
     for (int u = u_lo; u < u_hi && !failed; ++u) {
-        const int be = (int)be_next;
+        // a shared last window ends where the piece ends (segments are never shared)
+        const int be = (kMode == 2) ? (int)be_next : min((int)be_next, nb);
         if (u + 1 < u_hi) {
             be_next = ((kMode == 2) ? (long long)__ldg(a.seg_bend + u + 1) : unit_begin<kMode>(a, u + 2)) - B0;
         }
         // destination rows of this unit (accumulator rows 2*tid and 2*tid+1)
         int dst_row_lo = -1, dst_row_hi = -1;
         float* cbase = a.C;
-        if (kMode == 0) {
+        const bool shared_head = head_partial && u == u_lo;
+        const bool shared_tail = tail_partial && u == u_hi - 1;
+        if (kMode != 2 && (shared_head || shared_tail)) {
+            // partial tile: slot 2*gid for the unit this group entered through, 2*gid+1 for the one it leaves through
+            cbase = a.scratch + (size_t)(2 * gid + (shared_head ? 0 : 1)) * kWindowRows * N;
+            dst_row_lo = 2 * tid; dst_row_hi = dst_row_lo + 1;
+        } else if (kMode == 0) {
             dst_row_lo = u * kWindowRows + 2 * tid; dst_row_hi = dst_row_lo + 1;
             if (dst_row_lo >= a.M) dst_row_lo = -1;
             if (dst_row_hi >= a.M) dst_row_hi = -1;
@@ -343,6 +391,52 @@ tile_spmm_gather4_kernel(const __grid_constant__ CUtensorMap bmap, TileArgs a, i
     }
 }
 
+// Adds the partial tiles of every window that several groups shared, in block order, and writes the
+// window's rows. One CTA per group; the CTA of the group in which a shared window begins owns it:
+// its own tail slot comes first, then the head slots of the groups that follow, up to the group in
+// which the window ends.
+template <int kMode>
+__global__ void __launch_bounds__(128)
+g4_chain_merge_kernel(TileArgs a, int groups_total)
+{
+    __shared__ int s_unit, s_last_group;
+    const int g = blockIdx.x;
+    if (threadIdx.x == 0) {
+        const long long total_w = a.total_blocks + a.num_units;
+        int us, ue; long long bs, be;
+        g4_cut<kMode>(a, total_w * g / groups_total, us, bs);
+        g4_cut<kMode>(a, total_w * (g + 1) / groups_total, ue, be);
+        const bool tail = ue < a.num_units && be > unit_begin<kMode>(a, ue);
+        const bool began_earlier = (ue == us) && bs > unit_begin<kMode>(a, us);
+        int unit = -1, last = g;
+        if (tail && !began_earlier) {
+            unit = ue;
+            const long long ub = unit_begin<kMode>(a, unit);
+            for (int h = g + 1; h < groups_total; ++h) {         // groups whose piece lies inside the window
+                last = h;
+                int he; long long hb;
+                g4_cut<kMode>(a, total_w * (h + 1) / groups_total, he, hb);
+                if (!(he == unit && hb > ub)) break;             // the window ends in group h
+            }
+        }
+        s_unit = unit; s_last_group = last;
+    }
+    __syncthreads();
+    const int unit = s_unit;
+    if (unit < 0) return;
+    const int last = s_last_group;
+    const int N = a.N;
+    const size_t tile = (size_t)kWindowRows * N;
+    for (int idx = threadIdx.x; idx < kWindowRows * N; idx += blockDim.x) {
+        const int r = idx / N, col = idx - r * N;
+        const int row = (kMode == 1) ? __ldg(a.win_rows + (size_t)unit * kWindowRows + r) : unit * kWindowRows + r;
+        if (row < 0 || row >= a.M) continue;
+        float acc = a.scratch[(size_t)(2 * g + 1) * tile + idx];
+        for (int h = g + 1; h <= last; ++h) acc += a.scratch[(size_t)(2 * h) * tile + idx];
+        a.C[(size_t)row * N + col] = acc;
+    }
+}
+
 // ---- host side ------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
@@ -386,35 +480,77 @@ static int env_int(const char* name, int fallback)
     return e ? std::atoi(e) : fallback;
 }
 
-template <bool kTF32, int kMode, int S, int D>
-static int launch_g4(const CUtensorMap& map, const TileArgs& a, int slices_total, cudaStream_t st, int* status)
+// Launch shape of the ring for one SpMM: slices per warp, ring depth, CTA shape and the number of
+// groups the work axis is cut into. One function so that the caller that sizes the scratch of the
+// partial tiles and the launcher agree.
+struct G4Config {
+    bool ok = false;
+    int slices_total = 0, S = 0, D = 0, wpg = 0, groups_per_cta = 0, warps = 0, ctas = 0;
+    size_t smem = 0;
+    long long groups = 0;
+};
+
+static G4Config g4_configure(bool tf32, int mode, const TileArgs& a)
 {
-    const int wpg = (slices_total + S - 1) / S;                     // warps per group
-    const int groups_per_cta = std::max(1, 4 / wpg);
-    const int warps = wpg * groups_per_cta;
-    const size_t smem = (size_t)warps * D * (S * kG4AtomBytes + kG4ValBytes + 8) + kG4AtomBytes;
-    constexpr size_t kSmemCap = 227 * 1024;                        // dynamic shared memory a CTA can have
-    if (smem > kSmemCap) return RA_ERR_UNSUPPORTED;
+    G4Config c;
+    const int row_bytes = a.ldb * (tf32 ? 4 : 2);
+    if (row_bytes % 16 != 0 || row_bytes > 2048 || row_bytes <= 0) return c;
+    c.slices_total = (row_bytes + 127) / 128;
+    // slices per warp and ring depth: measured defaults, RA_G4_SLICES / RA_G4_DEPTH override
+    c.S = env_int("RA_G4_SLICES", 0);
+    if (c.S != 1 && c.S != 2 && c.S != 4) c.S = (c.slices_total >= 4 && !tf32) ? 4 : (c.slices_total >= 2 ? 2 : 1);
+    c.D = env_int("RA_G4_DEPTH", 0);
+    if (c.D != 2 && c.D != 4 && c.D != 8) c.D = 4;
+    if (!tf32 && c.D < 4) c.D = 4;                  // the FP16 path consumes two stages at a time
+    c.wpg = (c.slices_total + c.S - 1) / c.S;       // warps per group
+    c.groups_per_cta = std::max(1, 4 / c.wpg);
+    c.warps = c.wpg * c.groups_per_cta;
+    c.smem = (size_t)c.warps * c.D * (c.S * kG4AtomBytes + kG4ValBytes + 8) + kG4AtomBytes;
+    constexpr size_t kSmemCap = 227 * 1024;         // dynamic shared memory a CTA can have
+    if (c.smem > kSmemCap || c.warps > 8) return c;
+    const long long weight = a.total_blocks + a.num_units;
+    const int ctas_per_sm = (int)std::max<size_t>(1, std::min<size_t>(16, (220 * 1024) / (c.smem + 1024)));
+    // groups per resident slot: the FP16 path on windows (even unit lengths) is fastest with one
+    // piece per resident group (C3 4.8 vs 5.1 ms); TF32 and the segment lists, whose pieces differ
+    // more in cost, with three
+    const int waves = std::max(1, env_int("RA_G4_WAVES", (!tf32 && mode != 2) ? 1 : 3));
+    long long groups = (long long)sm_count() * ctas_per_sm * c.groups_per_cta * waves;
+    groups = std::min(groups, std::max<long long>(1, weight / 48));
+    c.ctas = (int)((groups + c.groups_per_cta - 1) / c.groups_per_cta);
+    c.groups = (long long)c.ctas * c.groups_per_cta;
+    c.ok = true;
+    return c;
+}
+
+// Floats of scratch the window families need for the partial tiles of shared windows (two
+// tiles of 8 x N per group); 0 when the ring does not apply to the shape.
+long long tile_gather4_split_scratch_floats(bool tf32, int mode, const TileArgs& a)
+{
+    if (mode == 2 || env_int("RA_G4_SPLIT", 1) == 0) return 0;
+    const G4Config c = g4_configure(tf32, mode, a);
+    return c.ok ? 2ll * c.groups * kWindowRows * a.N : 0;
+}
+
+template <bool kTF32, int kMode, int S, int D>
+static int launch_g4(const CUtensorMap& map, const TileArgs& a, const G4Config& c, cudaStream_t st, int* status)
+{
     auto kern = tile_spmm_gather4_kernel<kTF32, kMode, S, D>;
     static std::atomic<unsigned long long> configured{0};
     RA_CUDA_TRY(configure_once_per_device(configured, [&]() {
         const size_t most = (size_t)8 * D * (S * kG4AtomBytes + kG4ValBytes + 8) + kG4AtomBytes;   // 8 warps
-        return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)std::min(most, kSmemCap));
+        return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)std::min<size_t>(most, 227 * 1024));
     }));
-    const long long weight = a.total_blocks + a.num_units;
-    const int ctas_per_sm = (int)std::max<size_t>(1, std::min<size_t>(16, (220 * 1024) / (smem + 1024)));
-    // groups per resident slot: the FP16 path on windows (even unit lengths) is fastest with one
-    // range per resident group (C3 4.8 vs 5.1 ms); TF32 and the segment lists, whose ranges differ
-    // more in cost, with three
-    const int waves = std::max(1, env_int("RA_G4_WAVES", (!kTF32 && kMode != 2) ? 1 : 3));
-    long long groups = (long long)sm_count() * ctas_per_sm * groups_per_cta * waves;
-    groups = std::min(groups, std::max<long long>(1, weight / 48));
-    const int ctas = (int)((groups + groups_per_cta - 1) / groups_per_cta);
-    groups = (long long)ctas * groups_per_cta;
-    kern<<<ctas, warps * 32, smem, st>>>(map, a, slices_total, wpg, (int)groups, status,
-                                         (unsigned)std::max(0, env_int("RA_G4_WAIT_HINT_NS", 0)),
-                                         env_int("RA_G4_L2POLICY", 1));
+    // windows may be shared between groups when the caller gave room for the partial tiles
+    const bool split = kMode != 2 && env_int("RA_G4_SPLIT", 1) != 0 && a.scratch != nullptr &&
+                       a.scratch_floats >= 2ll * c.groups * kWindowRows * a.N;
+    kern<<<c.ctas, c.warps * 32, c.smem, st>>>(map, a, c.slices_total, c.wpg, (int)c.groups, status,
+                                               (unsigned)std::max(0, env_int("RA_G4_WAIT_HINT_NS", 0)),
+                                               env_int("RA_G4_L2POLICY", 1), split ? 1 : 0);
     RA_KERNEL_CHECK();
+    if (split) {
+        g4_chain_merge_kernel<(kMode == 2 ? 0 : kMode)><<<(unsigned)c.groups, 128, 0, st>>>(a, (int)c.groups);
+        RA_KERNEL_CHECK();
+    }
     return RA_OK;
 }
 
@@ -424,20 +560,13 @@ static int launch_g4(const CUtensorMap& map, const TileArgs& a, int slices_total
 template <bool kTF32, int kMode>
 int launch_tile_gather4(const TileArgs& a, const void* B, long long K, cudaStream_t st, int* status)
 {
-    constexpr int elem = kTF32 ? 4 : 2;
-    const int row_bytes = a.ldb * elem;
-    if (row_bytes % 16 != 0 || !aligned16(B) || K <= 0 || K >= (1ll << 31) || row_bytes > 2048) return RA_ERR_UNSUPPORTED;
-    const int slices_total = (row_bytes + 127) / 128;
+    if (!aligned16(B) || K <= 0 || K >= (1ll << 31)) return RA_ERR_UNSUPPORTED;
+    const G4Config c = g4_configure(kTF32, kMode, a);
+    if (!c.ok) return RA_ERR_UNSUPPORTED;
     CUtensorMap map;
     const int rc = make_b_map(&map, B, kTF32, K, a.ldb);
     if (rc != RA_OK) return rc;
-    // slices per warp and ring depth: measured defaults, RA_G4_SLICES / RA_G4_DEPTH override
-    int S = env_int("RA_G4_SLICES", 0);
-    if (S != 1 && S != 2 && S != 4) S = (slices_total >= 4 && !kTF32) ? 4 : (slices_total >= 2 ? 2 : 1);
-    int D = env_int("RA_G4_DEPTH", 0);
-    if (D != 2 && D != 4 && D != 8) D = 4;
-    if (!kTF32 && D < 4) D = 4;                     // the FP16 path consumes two stages at a time
-#define RA_G4_CASE(SS, DD) if (S == SS && D == DD) return launch_g4<kTF32, kMode, SS, DD>(map, a, slices_total, st, status)
+#define RA_G4_CASE(SS, DD) if (c.S == SS && c.D == DD) return launch_g4<kTF32, kMode, SS, DD>(map, a, c, st, status)
     RA_G4_CASE(1, 2); RA_G4_CASE(1, 4); RA_G4_CASE(1, 8); RA_G4_CASE(2, 2); RA_G4_CASE(2, 4); RA_G4_CASE(2, 8);
     RA_G4_CASE(4, 2); RA_G4_CASE(4, 4); RA_G4_CASE(4, 8);
 #undef RA_G4_CASE

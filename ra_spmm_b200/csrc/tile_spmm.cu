@@ -999,22 +999,31 @@ static int launch_tile(const TileArgs& a, const void* B, bool staged, cudaStream
         groups = std::min(groups, std::max<long long>(1, weight / 48));
         const int ctas = (int)((groups + groups_per_cta - 1) / groups_per_cta);
         groups = (long long)ctas * groups_per_cta;
-        // Engine choice. tcgen05 / TMEM path (FP16 only): measured on B200 1.2-1.5x faster than the
-        // per-warp rings at N = 128 (one full 128-feature panel per MMA), no better at other widths.
-        // TMA gather ring (tile_gather4.cu): faster than the cp.async ring on every other shape it
-        // covers (C3 FP16 N=256 4.9 vs 6.4 ms, C4 TF32 N=64 4.4 vs 5.0 ms). RA_TILE_TC5=1/0 and
-        // RA_TILE_G4=1/0 force an engine on or off.
+        // Engine choice, from full-size measurements on B200 (ms, TMA gather ring / cp.async ring / tcgen05):
+        //   FP16  N=256: configuration 3 COMMUNITY_TC 5.0 / 6.4 / -, configuration 5 10.2 / 13.4 / -
+        //         N=128: configuration 3 4.0 / 3.9 / 5.7, configuration 5 6.1 / 7.0 / 7.4, configuration 2 0.69 / 1.72 / 1.16
+        //         N=64 : configuration 4 TC_DIRECT 4.9 / 11.4 / -
+        //   TF32  N=64 : configuration 4 SEGMENT_HYBRID 4.7 / 5.0, configuration 3 4.3 / 4.6
+        //         N=128: configuration 3 8.5 / 9.2, configuration 2 0.93 / 1.13 (SEGMENT_HYBRID on 4: 9.2 / 8.9)
+        //         N=256: configuration 3 17.3 / 15.9, configuration 4 19.9 / 19.0
+        //   a few thousand blocks (configuration 1): 0.039 / 0.026
+        // So: the TMA ring for FP16 and for TF32 rows up to 512 bytes, the cp.async ring for wider TF32
+        // rows, for small matrices and for rows that are not whole 128-byte slices (N=47: 4.9 vs 3.6).
+        // The tcgen05 / TMEM kernel (FP16, N <= 512) was ahead of the rings at N=128 before they got
+        // their deeper stages and index batches; it is kept behind RA_TILE_TC5=1.
+        // RA_TILE_G4=1/0 forces the TMA ring on or off.
         const char* tc5_env = std::getenv("RA_TILE_TC5");
-        const bool tc5_auto = a.N > 96 && a.N <= 128;
-        const bool use_tc5 = !kZC && !padded && !kTF32 && a.N <= 512 && (tc5_env ? (tc5_env[0] == '1') : tc5_auto);
+        const bool use_tc5 = !kZC && !padded && !kTF32 && a.N <= 512 && tc5_env && tc5_env[0] == '1';
         const char* g4_env = std::getenv("RA_TILE_G4");
-        // a warp of the TMA ring has at most three blocks in flight, so it walks one unit slower than
-        // a warp of the 8-stage cp.async ring: units of thousands of blocks (hub windows of TC_DIRECT /
-        // COMMUNITY_TC on power-law graphs) stay on the cp.async ring
-        // rows that are not whole 128-byte slices (the 47-class GCN output, padded to 48 halves)
-        // straddle the TMA boxes and measured slower there (4.9 vs 3.6 ms)
-        const bool g4_auto = !use_tc5 && a.max_unit_blocks <= 1024 && (kMode == 2 || !kTF32 || a.N >= 256) &&
-                             (a.ldb * elem) % 128 == 0;
+        // The TMA ring shares windows between groups (partial tiles in scratch, merged in block order),
+        // so hub windows of thousands of blocks are no obstacle. Without room for the partial tiles
+        // (RA_G4_SPLIT=0) a warp walks a long window alone with three blocks in flight, and the cp.async
+        // ring keeps those shapes.
+        const bool shares_windows = kMode != 2 && a.scratch != nullptr && a.scratch_floats > 0;
+        const bool whole_units_ok = kMode == 2 || shares_windows || a.max_unit_blocks <= 1024;
+        const long long min_weight = std::getenv("RA_G4_MIN_WEIGHT") ? std::atoll(std::getenv("RA_G4_MIN_WEIGHT")) : 16384ll;
+        const bool g4_auto = !use_tc5 && whole_units_ok && a.total_blocks + a.num_units >= min_weight &&
+                             (!kTF32 || a.N <= 128) && (a.ldb * elem) % 128 == 0;
         const bool use_g4 = !kZC && (g4_env ? (g4_env[0] == '1') : g4_auto);
         if (use_g4) {
             const int rc = launch_tile_gather4<kTF32, kMode>(a, B, a.K, st, status);
@@ -1151,7 +1160,17 @@ extern "C" int ra_tile_plan_run(RaTilePlan* p, int precision, const void* d_B, i
     a.num_units = (p->kind == RA_TILE_SEGMENT_HYBRID) ? p->num_segments : p->num_windows;
     a.M = p->M; a.K = p->K; a.N = N; a.ldb = ldb; a.total_blocks = p->num_blocks;
     a.max_unit_blocks = (p->kind == RA_TILE_SEGMENT_HYBRID) ? std::min(p->max_window_blocks, kSegBlocks) : p->max_window_blocks;
-    a.C = d_C; a.scratch = p->d_scratch;
+    if (p->kind == RA_TILE_TC_DIRECT || p->kind == RA_TILE_COMMUNITY_TC) {
+        // room for the partial tiles of windows that the TMA ring shares between groups
+        const size_t need = (size_t)tile_gather4_split_scratch_floats(tf32, p->kind == RA_TILE_COMMUNITY_TC ? 1 : 0, a) * sizeof(float);
+        if (need > p->scratch_bytes) {
+            if (p->d_scratch) RA_CUDA_TRY(cudaFree(p->d_scratch));
+            p->d_scratch = nullptr; p->scratch_bytes = 0;
+            RA_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&p->d_scratch), need));
+            p->scratch_bytes = need;
+        }
+    }
+    a.C = d_C; a.scratch = p->d_scratch; a.scratch_floats = (long long)(p->scratch_bytes / sizeof(float));
 
     // RA_TC_STAGED=0 keeps the direct-load kernels, as in the reference (tc/ra_tc_direct.cu:837-838)
     const char* staged_env = std::getenv("RA_TC_STAGED");

@@ -230,6 +230,58 @@ def test_tcgen05_variant(cuda, kind, N, monkeypatch):
         monkeypatch.delenv("RA_TILE_TC5", raising=False)
 
 
+@pytest.mark.parametrize("split", ["1", "0"])
+@pytest.mark.parametrize("kind", ["tc", "ct", "sh"])
+@pytest.mark.parametrize("N", [32, 64, 128, 256, 512])
+def test_tma_gather_ring(cuda, kind, N, split, monkeypatch):
+    """RA_TILE_G4=1 runs the TMA gather ring at sizes the engine policy would give to the cp.async
+    ring; with RA_G4_SPLIT=1 the groups share windows (hub windows of 113 and 88 blocks cut across
+    several groups, partial tiles merged in block order), with 0 they take whole windows. Both
+    precisions against the float64 oracle on the rounded operands; reproducible; status clean."""
+    M, K = 333, 1200
+    rowptr, colind, vals = _mixed_matrix(M, K, seed=N + 9)
+    plan = KINDS[kind][1](torch.from_numpy(rowptr), torch.from_numpy(colind), torch.from_numpy(vals), M, K, N)
+    B = G.dense(K, N, N + 9)
+    Bd = B.to(cuda)
+    ci, va = to_dev(colind, cuda), to_dev(vals, cuda)
+    monkeypatch.setenv("RA_TILE_G4", "1")
+    monkeypatch.setenv("RA_G4_SPLIT", split)
+    try:
+        for tf32 in (False, True):
+            want = R.c_spmm_f64(rowptr, colind, vals, B.numpy(), 2 if tf32 else 1)
+            got = _run(kind, plan, Bd, tf32, ci, va)
+            torch.cuda.synchronize()
+            assert plan.device_status() == 0
+            assert rel_fro(got, want) < 1e-5, f"{kind} N={N} tf32={tf32} split={split}"
+            assert torch.equal(got, _run(kind, plan, Bd, tf32, ci, va))        # reproducible
+    finally:
+        monkeypatch.delenv("RA_TILE_G4", raising=False)
+        monkeypatch.delenv("RA_G4_SPLIT", raising=False)
+
+
+def test_tma_gather_ring_shares_one_long_window(cuda, monkeypatch):
+    """One window of 4,000 blocks between windows of a few blocks and empty windows: most groups
+    lie wholly inside the long window, so the merge walks a chain of many partial tiles."""
+    M, K, N = 64, 40000, 64
+    degs = np.zeros(M, dtype=np.int64)
+    degs[8:16] = 4000                  # window 1: 32,000 distinct columns = 4,000 blocks
+    degs[0] = 3; degs[40] = 17; degs[63] = 1
+    rowptr, colind, vals = small_csr(M, K, degs, seed=3)
+    B = G.dense(K, N, 3)
+    Bd = B.to(cuda)
+    monkeypatch.setenv("RA_TILE_G4", "1")
+    try:
+        for kind in ("tc", "ct"):
+            plan = KINDS[kind][1](torch.from_numpy(rowptr), torch.from_numpy(colind), torch.from_numpy(vals), M, K, N)
+            for tf32 in (False, True):
+                got = _run(kind, plan, Bd, tf32)
+                torch.cuda.synchronize()
+                assert plan.device_status() == 0
+                assert rel_fro(got, R.c_spmm_f64(rowptr, colind, vals, B.numpy(), 2 if tf32 else 1)) < 1e-5
+    finally:
+        monkeypatch.delenv("RA_TILE_G4", raising=False)
+
+
 # ---- zero-compressed TC_DIRECT (make_tc_direct_zc_plan) ---------------------------------
 def _zc_case(M, K, N, seed, cuda, unsorted=False):
     rowptr, colind, vals = _mixed_matrix(M, K, seed=seed, unsorted=unsorted)
@@ -276,8 +328,11 @@ def test_zc_outputs_equal_padded_plan(cuda, N):
     B = G.dense(K, N, N + 3).to(cuda)
     ref = RefTilePlan(3, rowptr, colind, vals, M, K, N) if ref_kernels() is not None else None
     import os
-    old = os.environ.get("RA_TILE_TC5")
-    os.environ["RA_TILE_TC5"] = "0"          # compare against the same engine (mma.sync ring)
+    # compare against the same engine and the same order of additions: no tcgen05 path, and the TMA
+    # ring with whole windows per group (shared windows add their partial tiles in another grouping)
+    saved = {k: os.environ.get(k) for k in ("RA_TILE_TC5", "RA_G4_SPLIT")}
+    os.environ["RA_TILE_TC5"] = "0"
+    os.environ["RA_G4_SPLIT"] = "0"
     try:
         for tf32 in (False, True):
             got = _run("tc", zc, B, tf32)
@@ -287,10 +342,11 @@ def test_zc_outputs_equal_padded_plan(cuda, N):
             if ref is not None:
                 assert rel_fro(got, ref.run(B, tf32)) < TOL_TILE
     finally:
-        if old is None:
-            os.environ.pop("RA_TILE_TC5", None)
-        else:
-            os.environ["RA_TILE_TC5"] = old
+        for k, v in saved.items():
+            if v is None:
+                os.environ.pop(k, None)
+            else:
+                os.environ[k] = v
 
 
 def test_zc_short_ranges_and_single_block(cuda):
