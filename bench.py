@@ -375,7 +375,10 @@ def build_balanced(torch, a, kernel, K, N, dev, b_dtype, B_dev, world, rank, arg
         return bounds, runner, log
     best = None
     for rnd in range(args.balance_rounds + 1):
-        times = gather_times(local_ms(torch, lambda: runner(B_dev), 5, 20))
+        # time enough launches to fill about 30 ms: a 0.1 ms block timed over 20 launches is noise
+        quick = local_ms(torch, lambda: runner(B_dev), 5, 10)
+        iters = int(min(400, max(20, 30.0 / max(quick, 1e-3))))
+        times = gather_times(local_ms(torch, lambda: runner(B_dev), 2, iters))
         log.append({"bounds": [int(x) for x in bounds], "ms": [round(t, 4) for t in times]})
         if best is None or max(times) < best[0]:
             best = (max(times), bounds.copy())

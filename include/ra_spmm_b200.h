@@ -282,8 +282,10 @@ RA_API int ra_tile_plan_info(const RaTilePlan* plan, RaTileInfo* out);
  * hand over an fp16 B directly (FP16 precision only). C is float32 [M,N].
  * Every plan kind runs through this call (a zero-compressed TC_DIRECT plan is
  * decoded inside the kernels). The plan's lazily grown scratch (fp16 copy of B,
- * split-segment partial tiles) makes a plan unsafe for two concurrent runs, as
- * in the reference (ra_common.h:607-609, 704-708). */
+ * partial tiles of split segments and of windows shared between groups of the
+ * TMA ring) makes a plan unsafe for two concurrent runs, as in the reference
+ * (ra_common.h:607-609, 704-708); it grows (cudaMalloc) on the first run at a
+ * given width, so make that run before any stream capture. */
 RA_API int ra_tile_plan_run(RaTilePlan* plan, int precision, const void* d_B, int b_dtype,
                             float* d_C, int N, void* stream);
 RA_API int ra_tile_plan_destroy(RaTilePlan* plan);
