@@ -244,28 +244,36 @@ class Runner:
         self.tf32 = kernel.endswith("_TF32")
         self.plan = None
         self.launches = 1
-        torch.cuda.synchronize()
-        t_plan = time.perf_counter()
+        builders = {
+            "ZERO_OVERHEAD_CSR": lambda: ra_spmm.make_zero_overhead_plan(self.rp, self.M, K),
+            "TC_DIRECT": lambda: ra_spmm.make_tc_direct_plan(self.rp, self.ci, self.va, self.M, K, N),
+            "COMMUNITY_TC": lambda: ra_spmm.make_community_tc_plan(self.rp, self.ci, self.va, self.M, K, N),
+            "SEGMENT_HYBRID": lambda: ra_spmm.make_segment_hybrid_plan(self.rp, self.ci, self.va, self.M, K, N),
+        }
+        if fam not in builders and fam != "CSR_DIRECT":
+            raise SystemExit(f"unknown kernel {kernel}")
+        # wall-clock time of the plan build from device-resident CSR (for COMMUNITY_TC it includes the
+        # locality sort, for the tile families the window sort and the packing of the blocks): the
+        # faster of two builds, since the first one of a process also loads the builder kernels
+        self.plan_ms = 0.0
+        if fam in builders:
+            times = []
+            for _ in range(2):
+                self.plan = None
+                torch.cuda.synchronize()
+                t_plan = time.perf_counter()
+                self.plan = builders[fam]()
+                torch.cuda.synchronize()
+                times.append((time.perf_counter() - t_plan) * 1e3)
+            self.plan_ms = min(times)
         if fam == "ZERO_OVERHEAD_CSR":
-            self.plan = ra_spmm.make_zero_overhead_plan(self.rp, self.M, K)
             data = (self.plan.num_chunks > 0) + (self.plan.num_small > 0)
             long_rows = N >= 256 and self.plan.num_chunks >= 16 * self.plan.num_small
             if data == 2 and N in (32, 64, 128, 256, 512) and not long_rows:
                 data = 1                           # chunks and small rows share one launch at these widths
             self.launches = data + (self.plan.num_zero_rows > 0)
-        elif fam == "TC_DIRECT":
-            self.plan = ra_spmm.make_tc_direct_plan(self.rp, self.ci, self.va, self.M, K, N)
-        elif fam == "COMMUNITY_TC":
-            self.plan = ra_spmm.make_community_tc_plan(self.rp, self.ci, self.va, self.M, K, N)
         elif fam == "SEGMENT_HYBRID":
-            self.plan = ra_spmm.make_segment_hybrid_plan(self.rp, self.ci, self.va, self.M, K, N)
             self.launches = 1 + (self.plan.num_split_windows > 0)
-        elif fam != "CSR_DIRECT":
-            raise SystemExit(f"unknown kernel {kernel}")
-        torch.cuda.synchronize()
-        # wall-clock time of the plan build from device-resident CSR (for COMMUNITY_TC it includes
-        # the locality sort, for the tile families the window sort and the packing of the blocks)
-        self.plan_ms = (time.perf_counter() - t_plan) * 1e3
         if fam in ("TC_DIRECT", "COMMUNITY_TC", "SEGMENT_HYBRID") and not self.tf32 and b_dtype == "float32":
             self.launches += 1                     # per-call fp32 -> fp16 conversion of B
         self.fam = fam

@@ -155,6 +155,11 @@ tile_spmm_gather4_kernel(const __grid_constant__ CUtensorMap bmap, TileArgs a, i
         head_partial = us < a.num_units && bs > unit_begin<kMode>(a, us);
         u_lo = us; u_hi = tail_partial ? ue + 1 : ue;
         B0 = bs; B1 = be;
+        if (part == 0 && lane == 0) {
+            // for the merge: the window this group entered through and the one it leaves through (-1: none)
+            int2* shared_windows = reinterpret_cast<int2*>(a.scratch + (size_t)2 * groups_total * kWindowRows * a.N);
+            shared_windows[gid] = make_int2(head_partial ? us : -1, tail_partial ? ue : -1);
+        }
     } else {
         u_lo = unit_lower_bound<kMode>(a, total_w * gid / groups_total);
         u_hi = unit_lower_bound<kMode>(a, total_w * (gid + 1) / groups_total);
@@ -399,32 +404,13 @@ template <int kMode>
 __global__ void __launch_bounds__(128)
 g4_chain_merge_kernel(TileArgs a, int groups_total)
 {
-    __shared__ int s_unit, s_last_group;
     const int g = blockIdx.x;
-    if (threadIdx.x == 0) {
-        const long long total_w = a.total_blocks + a.num_units;
-        int us, ue; long long bs, be;
-        g4_cut<kMode>(a, total_w * g / groups_total, us, bs);
-        g4_cut<kMode>(a, total_w * (g + 1) / groups_total, ue, be);
-        const bool tail = ue < a.num_units && be > unit_begin<kMode>(a, ue);
-        const bool began_earlier = (ue == us) && bs > unit_begin<kMode>(a, us);
-        int unit = -1, last = g;
-        if (tail && !began_earlier) {
-            unit = ue;
-            const long long ub = unit_begin<kMode>(a, unit);
-            for (int h = g + 1; h < groups_total; ++h) {         // groups whose piece lies inside the window
-                last = h;
-                int he; long long hb;
-                g4_cut<kMode>(a, total_w * (h + 1) / groups_total, he, hb);
-                if (!(he == unit && hb > ub)) break;             // the window ends in group h
-            }
-        }
-        s_unit = unit; s_last_group = last;
-    }
-    __syncthreads();
-    const int unit = s_unit;
-    if (unit < 0) return;
-    const int last = s_last_group;
+    const int2* shared_windows = reinterpret_cast<const int2*>(a.scratch + (size_t)2 * groups_total * kWindowRows * a.N);
+    const int2 mine = shared_windows[g];
+    const int unit = mine.y;
+    if (unit < 0 || mine.x == unit) return;                      // no window begins here and continues in the next group
+    int last = g + 1;                                            // groups g+1 .. last hold the rest of the window
+    while (last + 1 < groups_total && shared_windows[last].y == unit) ++last;
     const int N = a.N;
     const size_t tile = (size_t)kWindowRows * N;
     for (int idx = threadIdx.x; idx < kWindowRows * N; idx += blockDim.x) {
@@ -528,7 +514,7 @@ long long tile_gather4_split_scratch_floats(bool tf32, int mode, const TileArgs&
 {
     if (mode == 2 || env_int("RA_G4_SPLIT", 1) == 0) return 0;
     const G4Config c = g4_configure(tf32, mode, a);
-    return c.ok ? 2ll * c.groups * kWindowRows * a.N : 0;
+    return c.ok ? 2ll * c.groups * kWindowRows * a.N + 2ll * c.groups : 0;   // partial tiles + one int2 per group
 }
 
 template <bool kTF32, int kMode, int S, int D>
@@ -540,9 +526,17 @@ static int launch_g4(const CUtensorMap& map, const TileArgs& a, const G4Config& 
         const size_t most = (size_t)8 * D * (S * kG4AtomBytes + kG4ValBytes + 8) + kG4AtomBytes;   // 8 warps
         return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)std::min<size_t>(most, 227 * 1024));
     }));
-    // windows may be shared between groups when the caller gave room for the partial tiles
-    const bool split = kMode != 2 && env_int("RA_G4_SPLIT", 1) != 0 && a.scratch != nullptr &&
-                       a.scratch_floats >= 2ll * c.groups * kWindowRows * a.N;
+    // Windows are shared between groups when the caller gave room for the partial tiles and whole
+    // windows would leave the pieces uneven: the longest window is more than an eighth of a piece.
+    // With many short windows per piece the groups keep whole windows: they then all start at a window
+    // boundary and sweep the (sorted) columns of their windows at the same pace, which the L2 rewards
+    // (configuration 3 TC_DIRECT on one GPU: 9.3 GB of DRAM reads against 21.3 GB with arbitrary cuts,
+    // same time), and there is no merge launch.
+    const long long piece = (a.total_blocks + a.num_units) / std::max<long long>(1, c.groups);
+    const int split_env = env_int("RA_G4_SPLIT", 1);
+    const bool uneven = split_env == 2 || ((long long)a.max_unit_blocks + 1) * 8 > piece;
+    const bool split = kMode != 2 && split_env != 0 && uneven && a.scratch != nullptr &&
+                       a.scratch_floats >= 2ll * c.groups * kWindowRows * a.N + 2ll * c.groups;
     kern<<<c.ctas, c.warps * 32, c.smem, st>>>(map, a, c.slices_total, c.wpg, (int)c.groups, status,
                                                (unsigned)std::max(0, env_int("RA_G4_WAIT_HINT_NS", 0)),
                                                env_int("RA_G4_L2POLICY", 1), split ? 1 : 0);
