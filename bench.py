@@ -720,13 +720,18 @@ def main():
         # (forward + backward + Adam; NCCL all-gather of each layer's row slabs at N > 1),
         # once with the routed kernels (FP16 tile path) and once all in fp32 through CSR_DIRECT
         from ra_spmm_b200 import gcn_bench
-        for gk in ("routed", "CSR_DIRECT"):
+        # and once with layer 1 associated the other way, (A X) W1: the same model, but the first SpMM
+        # runs at the input width and its backward needs none (reported beside, not instead of, the
+        # reference harness's order)
+        for gk, order in (("routed", "reference"), ("CSR_DIRECT", "reference"), ("routed", "aggregate-first")):
             try:
                 gargs = gcn_bench.parse_args(["--scale", str(args.scale), "--steps", "10", "--warmup", "3",
-                                              "--kernel", gk, "--panels", str(args.gcn_panels if dist_on else 1)])
+                                              "--kernel", gk, "--order", order,
+                                              "--panels", str(args.gcn_panels if dist_on else 1)])
                 g = gcn_bench.measure(gargs, world, rank, dev)
                 if rank == 0:
-                    also.append({"config": "C5", "kernel": f"2-layer GCN step, {gk} SpMM (" +
+                    also.append({"config": "C5", "order": order,
+                                 "kernel": f"2-layer GCN step, {gk} SpMM (" +
                                  ", ".join(f"N={k}: {v}" for k, v in sorted(g["config"]["labels"].items())) + ")",
                                  "gcn_step_ms": g["value"], "spmm_gflops": g["spmm_gflops"], "loss": g["loss"],
                                  "steps": g["steps"], "warmup": g["warmup"], "workload": g["config"]["workload"],

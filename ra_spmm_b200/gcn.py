@@ -83,7 +83,7 @@ class GraphOperator:
     "TC_DIRECT[_TF32]", "COMMUNITY_TC[_TF32]", "SEGMENT_HYBRID[_TF32]"."""
 
     def __init__(self, rowptr: np.ndarray, colind: np.ndarray, vals: np.ndarray, K: int,
-                 device, kernel: str = "routed"):
+                 device, kernel: str = "routed", labels=None):
         from . import ra_spmm
         self.m = ra_spmm
         self.device = torch.device(device)
@@ -93,7 +93,8 @@ class GraphOperator:
         self.va = torch.from_numpy(np.ascontiguousarray(vals, dtype=np.float32)).to(self.device)
         self.kernel = kernel
         self._plans = {}
-        self.labels = {}
+        self.labels = dict(labels or {})      # width -> kernel label; preset labels skip the router (chunk operators
+                                              # take the decision made on the whole row block)
 
     def _resolve(self, N: int) -> str:
         if self.kernel != "routed":
@@ -158,12 +159,21 @@ class RowSharding:
     operator's column indices are remapped once (`remap_columns`) to address that
     layout, so no compaction pass is needed."""
 
-    def __init__(self, bounds, rank: int = 0, world: int = 1, group=None):
+    def __init__(self, bounds, rank: int = 0, world: int = 1, group=None, chunks: int = 1):
         self.bounds = [int(b) for b in bounds]
         self.rank, self.world, self.group = rank, world, group
         self.max_rows = max((self.bounds[i + 1] - self.bounds[i] for i in range(world)), default=0)
         self.comm_bytes = 0
         self._slabs = {}
+        # Row chunks: every rank's slab is cut into `chunks` runs of rows, chunk j of all ranks is
+        # gathered on its own, and the operator is split by the chunk that owns the column
+        # (`split_columns`). The SpMM of chunk j then runs while chunk j+1 is still on the wire, with
+        # rows of the operand at their full width.
+        self.chunks = max(1, int(chunks)) if world > 1 else 1
+        self.chunk_starts = [[(self.bounds[r + 1] - self.bounds[r]) * j // self.chunks for j in range(self.chunks + 1)]
+                             for r in range(world)]
+        self.max_chunk_rows = [max((cs[j + 1] - cs[j] for cs in self.chunk_starts), default=0)
+                               for j in range(self.chunks)]
 
     @property
     def rows(self):
@@ -181,6 +191,38 @@ class RowSharding:
         b = np.asarray(self.bounds, dtype=np.int64)
         owner = np.searchsorted(b, colind, side="right") - 1
         return (owner * self.max_rows + (colind - b[owner])).astype(np.int32)
+
+    def split_columns(self, rowptr: np.ndarray, colind: np.ndarray, vals: np.ndarray):
+        """The rank's row block cut by the chunk that owns each column: a list of `chunks` tuples
+        (rowptr, colind, vals, K) whose columns address the gathered operand of that chunk
+        (rank r's rows of chunk j start at r * max_chunk_rows[j])."""
+        k = self.chunks
+        starts = np.array([self.bounds[r] + self.chunk_starts[r][j] for r in range(self.world) for j in range(k)],
+                          dtype=np.int64)
+        idx = np.searchsorted(starts, colind, side="right") - 1
+        owner, chunk = idx // k, idx % k
+        local = colind.astype(np.int64) - starts[idx]
+        rows = np.repeat(np.arange(rowptr.size - 1, dtype=np.int64), np.diff(rowptr))
+        out = []
+        for j in range(k):
+            sel = np.flatnonzero(chunk == j)
+            rp = np.zeros(rowptr.size, dtype=np.int64)
+            np.cumsum(np.bincount(rows[sel], minlength=rowptr.size - 1), out=rp[1:])
+            ci = (owner[sel] * self.max_chunk_rows[j] + local[sel]).astype(np.int32)
+            out.append((rp.astype(np.int32), ci, np.ascontiguousarray(vals[sel]), self.world * self.max_chunk_rows[j]))
+        return out
+
+    def all_gather_chunk(self, local: torch.Tensor, j: int, dtype=None, width=None):
+        """Starts the gather of row chunk j of every rank's slab; returns (operand, work handle)."""
+        dtype = dtype or local.dtype
+        width = width or local.shape[1]
+        c0, c1 = self.chunk_starts[self.rank][j], self.chunk_starts[self.rank][j + 1]
+        src = torch.zeros((self.max_chunk_rows[j], width), dtype=dtype, device=local.device)
+        src[: c1 - c0, : local.shape[1]].copy_(local[c0:c1])
+        full = torch.empty((self.world * self.max_chunk_rows[j], width), dtype=dtype, device=local.device)
+        work = dist.all_gather_into_tensor(full, src, group=self.group, async_op=True)
+        self.comm_bytes += full.numel() * full.element_size()
+        return full, work
 
     def _padded_slab(self, local: torch.Tensor, dtype, width: int, keep: bool = True) -> torch.Tensor:
         """This rank's slab in the gather layout: max_rows x width in `dtype`, filled from `local`
@@ -221,6 +263,18 @@ def _gather_and_multiply(local, spmm: Callable, sharding: RowSharding, fmt, pane
     multiple of 16); all panel gathers are queued at once and the SpMM of a panel starts as soon
     as its own gather has landed, so it overlaps the gathers behind it."""
     n = local.shape[1]
+    if isinstance(spmm, (list, tuple)):
+        # row chunks: one operator per chunk; all gathers are queued, chunk j is multiplied as soon
+        # as it has landed and the partial results are added in chunk order
+        assert len(spmm) == sharding.chunks, "one operator per row chunk"
+        dtype, width = fmt(n) if fmt is not None else (local.dtype, n)
+        pending = [sharding.all_gather_chunk(local, j, dtype, width) for j in range(sharding.chunks)]
+        out = None
+        for op, (full, work) in zip(spmm, pending):
+            work.wait()
+            part = op(full)
+            out = part if out is None else out.add_(part)
+        return out[:, :n].contiguous() if width != n else out
     if sharding.world > 1 and panels > 1 and n % (16 * panels) == 0 and n // panels >= 32:
         w = n // panels
         pending = []
@@ -255,6 +309,8 @@ class _ShardedSpMM(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, grad_out):
+        if not ctx.needs_input_grad[0]:              # the operand is an input of the model: nothing to propagate
+            return None, None, None, None, None, None, None
         g = _gather_and_multiply(grad_out.contiguous(), ctx.spmm_t, ctx.sharding, ctx.fmt_t, ctx.panels)
         return g, None, None, None, None, None, None
 
@@ -271,14 +327,22 @@ class GCN2(nn.Module):
     def __init__(self, in_dim: int, hidden: int, out_dim: int, spmm: Callable,
                  spmm_t: Optional[Callable] = None, sharding: Optional[RowSharding] = None,
                  operand_format: Optional[Callable] = None, operand_format_t: Optional[Callable] = None,
-                 panels: int = 1):
+                 panels: int = 1, aggregate_first: bool = False):
         super().__init__()
         self.lin1 = nn.Linear(in_dim, hidden, bias=False)
         self.lin2 = nn.Linear(hidden, out_dim, bias=False)
+        # aggregate_first: layer 1 as (A X) W1 instead of A (X W1) - the same layer, associated the
+        # other way. With in_dim < hidden the SpMM (and its gather) runs at the narrower width, and
+        # because X needs no gradient the backward of layer 1 has no SpMM at all: dW1 = (A X)^T g.
+        # Off by default: the reference harness multiplies by W first.
+        self.aggregate_first = aggregate_first
         _attach(self, spmm, spmm_t, sharding, operand_format, operand_format_t, panels)
 
     def forward(self, X_local):
-        h = F.relu(self.aggregate(self.lin1(X_local)))
+        if self.aggregate_first:
+            h = F.relu(self.lin1(self.aggregate(X_local)))
+        else:
+            h = F.relu(self.aggregate(self.lin1(X_local)))
         return self.aggregate(self.lin2(h))
 
 

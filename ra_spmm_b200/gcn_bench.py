@@ -38,6 +38,12 @@ def parse_args(argv=None):
     ap.add_argument("--panels", type=int, default=1,
                     help="multi-GPU: gather wide operands in this many column panels and start each panel's "
                          "SpMM when its own gather has landed")
+    ap.add_argument("--order", default="reference", choices=["reference", "aggregate-first"],
+                    help="layer 1 as A (X W1), the reference harness's order, or as (A X) W1: the same layer with the "
+                         "SpMM at the input width and no SpMM in its backward (X needs no gradient)")
+    ap.add_argument("--chunks", type=int, default=1,
+                    help="multi-GPU: gather every slab in this many runs of rows and split the operator by the "
+                         "chunk that owns the column, so the SpMM of a chunk overlaps the gather of the next")
     return ap.parse_args(argv)
 
 
@@ -54,16 +60,24 @@ def measure(args, world: int, rank: int, dev):
     bounds = P.nnz_balanced_row_splits(a.rowptr, world)
     r0, r1 = int(bounds[rank]), int(bounds[rank + 1])
     rp, ci, va = P.row_block(a.rowptr, a.colind, a.vals, r0, r1)
-    sharding = RowSharding(bounds, rank, world)
+    sharding = RowSharding(bounds, rank, world, chunks=args.chunks)
     # A^T = A: one operator both ways; its columns address the padded gathered operand
     op = GraphOperator(rp, sharding.remap_columns(ci), va, sharding.gathered_rows, dev, kernel=args.kernel)
+    spmm = op.matmul
+    if sharding.chunks > 1:
+        # the routing decision is the one of the whole row block; one operator per row chunk
+        for width in (256, 47, 100):
+            op.operand_format(width)
+        chunk_ops = [GraphOperator(crp, cci, cva, cK, dev, kernel=args.kernel, labels=op.labels)
+                     for crp, cci, cva, cK in sharding.split_columns(rp, ci, va)]
+        spmm = [o.matmul for o in chunk_ops]
     g = torch.Generator().manual_seed(123)
     X = torch.randn((a.M, 100), generator=g)[r0:r1].to(dev)
     y = torch.randint(0, 47, (a.M,), generator=g)[r0:r1].to(dev)
     torch.manual_seed(123)
-    model = GCN2(100, 256, 47, op.matmul, sharding=sharding,
+    model = GCN2(100, 256, 47, spmm, sharding=sharding,
                  operand_format=op.operand_format if args.gather == "kernel" else None,
-                 panels=args.panels).to(dev)
+                 panels=args.panels, aggregate_first=args.order == "aggregate-first").to(dev)
     opt = torch.optim.Adam(model.parameters(), lr=1e-2)
 
     for _ in range(max(args.warmup, 1)):
@@ -84,7 +98,7 @@ def measure(args, world: int, rank: int, dev):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     spmm_ms = None
-    if args.breakdown:
+    if args.breakdown and sharding.chunks == 1:
         calls = []
         inner = op.matmul
 
@@ -102,14 +116,15 @@ def measure(args, world: int, rank: int, dev):
     line = None
     if rank == 0:
         nnz = a.nnz
-        spmm_flops = 2.0 * nnz * (256 + 47) * 2            # forward + backward of the two SpMM sites
+        # forward + backward of the two SpMM sites; aggregate-first: width 100 forward only at site 1
+        spmm_flops = 2.0 * nnz * ((256 + 47) * 2 if args.order == "reference" else (100 + 47 * 2))
         line = {"metric": "gcn_step_ms_warm", "value": ms, "unit": "ms", "higher_is_better": False,
                 "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 1),
                 "spmm_gflops": spmm_flops / (ms * 1e-3) / 1e9, "loss": float(loss),
                 "config": {"workload": f"2-layer GCN on SBM {a.M} nodes, nnz {nnz}, 100->256->47", "kernel": args.kernel,
                            "labels": op.labels, "allgather_bytes_per_step_per_rank": sharding.comm_bytes // args.steps,
                            "partition": f"{world} nnz-balanced row blocks, all-gather before each SpMM", "gather": args.gather,
-                           "panels": args.panels}}
+                           "panels": args.panels, "chunks": sharding.chunks, "order": args.order}}
         if spmm_ms is not None:
             line["breakdown"] = spmm_ms
         if args.cpu_baseline and world == 1:

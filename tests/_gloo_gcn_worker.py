@@ -74,6 +74,35 @@ assert torch.allclose(whole, in_panels, rtol=1e-6, atol=1e-6)
 assert torch.equal(sharded_spmm(H[:, :40].contiguous(), op, op, sh, panels=4),      # too narrow: falls back to one gather
                    sharded_spmm(H[:, :40].contiguous(), op, op, sh))
 
+# ---- row chunks: the slab is gathered in 3 runs of rows, the operator is split by the chunk that
+# owns the column, the partial products are added; with and without the fp16 operand format, and a
+# whole training step ----
+sh3 = RowSharding(bounds, rank, world, chunks=3)
+ops3 = [cpu_op(*t) for t in sh3.split_columns(rp, ci, va)]
+assert sum(int(t[0][-1]) for t in sh3.split_columns(rp, ci, va)) == int(rp[-1])
+in_chunks = sharded_spmm(H, ops3, ops3, sh3)
+assert torch.allclose(whole, in_chunks, rtol=1e-5, atol=1e-5)
+H47 = torch.randn(r1 - r0, 47, generator=torch.Generator().manual_seed(300 + rank))
+ops3_f = [(lambda B, f=f: f(B.float())) for f in ops3]
+got3 = sharded_spmm(H47, ops3_f, ops3_f, sh3, operand_format=lambda n: (torch.float16, (n + 15) // 16 * 16))
+want3 = cpu_op(rp, sh.remap_columns(ci), va, sh.gathered_rows)(sh.all_gather_rows(H47.half().float()))
+assert got3.shape == (r1 - r0, 47) and torch.allclose(got3, want3, rtol=1e-5, atol=1e-5)
+torch.manual_seed(7)
+model3 = GCN2(100, 64, 47, ops3, sharding=sh3)
+loss3 = train_step(model3, torch.optim.Adam(model3.parameters(), lr=1e-2), X[r0:r1], y[r0:r1], a.M)
+assert abs(float(loss3) - float(loss)) < 1e-5, (float(loss3), float(loss))
+for p3, q in zip(model3.parameters(), model.parameters()):
+    assert torch.allclose(p3, q, rtol=1e-4, atol=1e-6)
+
+# ---- layer 1 associated the other way, (A X) W1: same loss and weights as A (X W1), sharded or not ----
+torch.manual_seed(7)
+af = GCN2(100, 64, 47, cpu_op(rp, sh.remap_columns(ci), va, sh.gathered_rows), sharding=sh, aggregate_first=True)
+loss_af = train_step(af, torch.optim.Adam(af.parameters(), lr=1e-2), X[r0:r1], y[r0:r1], a.M)
+assert abs(float(loss_af) - float(ref_loss)) < 1e-5, (float(loss_af), float(ref_loss))
+for pa, q in zip(af.parameters(), ref_model.parameters()):
+    assert torch.allclose(pa.grad, q.grad, rtol=1e-3, atol=1e-5)
+    assert torch.allclose(pa, q, rtol=1e-3, atol=1e-5)
+
 # ---- GraphSAGE (row-mean operator, not symmetric: the backward needs the transposed row block)
 # and GIN (raw adjacency, learnable eps) against the unsharded step ----
 from ra_spmm_b200.gcn import GIN2, SAGE2, aggregation_operator, transpose_csr   # noqa: E402
