@@ -485,8 +485,12 @@ static G4Config g4_configure(bool tf32, int mode, const TileArgs& a)
     // slices per warp and ring depth: measured defaults, RA_G4_SLICES / RA_G4_DEPTH override
     c.S = env_int("RA_G4_SLICES", 0);
     if (c.S != 1 && c.S != 2 && c.S != 4) c.S = (c.slices_total >= 4 && !tf32) ? 4 : (c.slices_total >= 2 ? 2 : 1);
+    // Ring depth: 4 stages; 8 for the FP16 path with one slice per warp (N <= 64). That kernel holds 16
+    // warps per SM by its registers whatever the ring costs, and with 1 KB stages four of them are too
+    // few bytes in flight when the rows come from DRAM (configuration 5 at N=64: 3.1 vs 7.9 ms); with
+    // wider slices 8 stages cost resident warps instead (35-150 % slower).
     c.D = env_int("RA_G4_DEPTH", 0);
-    if (c.D != 2 && c.D != 4 && c.D != 8) c.D = 4;
+    if (c.D != 2 && c.D != 4 && c.D != 8) c.D = (!tf32 && c.S == 1) ? 8 : 4;
     if (!tf32 && c.D < 4) c.D = 4;                  // the FP16 path consumes two stages at a time
     c.wpg = (c.slices_total + c.S - 1) / c.S;       // warps per group
     c.groups_per_cta = std::max(1, 4 / c.wpg);
