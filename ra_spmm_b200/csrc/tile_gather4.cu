@@ -471,7 +471,7 @@ static int env_int(const char* name, int fallback)
 // partial tiles and the launcher agree.
 struct G4Config {
     bool ok = false;
-    int slices_total = 0, S = 0, D = 0, wpg = 0, groups_per_cta = 0, warps = 0, ctas = 0;
+    int slices_total = 0, S = 0, D = 0, wpg = 0, groups_per_cta = 0, warps = 0, ctas = 0, waves = 1;
     size_t smem = 0;
     long long groups = 0;
 };
@@ -504,6 +504,7 @@ static G4Config g4_configure(bool tf32, int mode, const TileArgs& a)
     // piece per resident group (C3 4.8 vs 5.1 ms); TF32 and the segment lists, whose pieces differ
     // more in cost, with three
     const int waves = std::max(1, env_int("RA_G4_WAVES", (!tf32 && mode != 2) ? 1 : 3));
+    c.waves = waves;
     long long groups = (long long)sm_count() * ctas_per_sm * c.groups_per_cta * waves;
     groups = std::min(groups, std::max<long long>(1, weight / 48));
     c.ctas = (int)((groups + c.groups_per_cta - 1) / c.groups_per_cta);
@@ -522,7 +523,7 @@ long long tile_gather4_split_scratch_floats(bool tf32, int mode, const TileArgs&
 }
 
 template <bool kTF32, int kMode, int S, int D>
-static int launch_g4(const CUtensorMap& map, const TileArgs& a, const G4Config& c, cudaStream_t st, int* status)
+static int launch_g4(const CUtensorMap& map, const TileArgs& a, const G4Config& cfg, cudaStream_t st, int* status)
 {
     auto kern = tile_spmm_gather4_kernel<kTF32, kMode, S, D>;
     static std::atomic<unsigned long long> configured{0};
@@ -530,6 +531,18 @@ static int launch_g4(const CUtensorMap& map, const TileArgs& a, const G4Config& 
         const size_t most = (size_t)8 * D * (S * kG4AtomBytes + kG4ValBytes + 8) + kG4AtomBytes;   // 8 warps
         return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)std::min<size_t>(most, 227 * 1024));
     }));
+    // g4_configure counts the CTAs an SM holds by shared memory; registers can allow fewer (the FP16
+    // kernels use 126 per thread: 4 CTAs of 128 threads), and a grid of 5 CTAs per SM on 4 resident ones
+    // runs a last quarter wave on its own. Size the grid by what is really resident.
+    G4Config c = cfg;
+    int resident = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, kern, c.warps * 32, c.smem) == cudaSuccess && resident > 0) {
+        const long long fit = (long long)sm_count() * resident * c.groups_per_cta * c.waves;
+        if (fit < c.groups) {
+            c.ctas = (int)((fit + c.groups_per_cta - 1) / c.groups_per_cta);
+            c.groups = (long long)c.ctas * c.groups_per_cta;
+        }
+    }
     // Windows are shared between groups when the caller gave room for the partial tiles and whole
     // windows would leave the pieces uneven: the longest window is more than an eighth of a piece.
     // With many short windows per piece the groups keep whole windows: they then all start at a window
