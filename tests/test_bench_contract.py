@@ -35,7 +35,7 @@ import pytest  # noqa: E402
 @pytest.mark.gpu
 def test_gpu_arm_prints_one_contract_line_at_test_size():
     """The GPU arm end to end at 2^-7 of configuration 4: one JSON line with the roofline, CPU
-    baseline, end-to-end, clock, launch-count and parity keys, and a parity verdict that holds."""
+    baseline, end-to-end, clock, launch-count and parity keys, and a parity check that holds."""
     r = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--scale", str(2 ** -7), "--steps", "5", "--warmup", "3",
                         "--also", "off", "--inner-warmup", "3", "--inner-iters", "5"],
                        capture_output=True, text=True, timeout=900)
