@@ -1116,8 +1116,15 @@ extern "C" int ra_tile_plan_run(RaTilePlan* p, int precision, const void* d_B, i
 
     const void* Bop = d_B;
     // widths that are not a multiple of 16 get a padded fp16 copy of B (the conversion pass runs
-    // anyway), so they run on the staged kernel instead of the direct-load fallback
-    const int ldb = (!tf32 && b_dtype == RA_DTYPE_F32) ? ((N + 15) & ~15) : N;
+    // anyway), so they run on the staged kernel instead of the direct-load fallback. Where rounding
+    // the row up to whole 128-byte slices costs at most 40 % more bytes (N=47 -> 64, N=100 -> 128) the
+    // copy is padded that far and the TMA ring takes it: configuration 5, 3.1 vs 3.6 ms and 5.3 vs 7.5 ms.
+    int ldb = N;
+    if (!tf32 && b_dtype == RA_DTYPE_F32) {
+        ldb = (N + 15) & ~15;
+        const int slices = (N + 63) & ~63;
+        if (ldb % 64 != 0 && N > 32 && (long long)slices * 5 <= (long long)N * 7 && !(std::getenv("RA_TILE_PAD_SLICES") && std::getenv("RA_TILE_PAD_SLICES")[0] == '0')) ldb = slices;
+    }
     if (!tf32 && b_dtype == RA_DTYPE_F32) {
         const long long total = (long long)p->K * ldb;
         const size_t need = (size_t)total * sizeof(uint16_t);
